@@ -1,0 +1,810 @@
+// bf16 grouped GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A/B k-blocks into a 4-stage
+//               shared-memory ring (128-byte swizzle), signalled by mbarrier transaction counts;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, bf16 in, fp32
+//               accumulate in tensor memory); tcgen05.commit releases ring stages and publishes
+//               finished accumulators;
+//   warps 2-5   epilogue: tcgen05.ld of the accumulator (one TMEM lane = one output row per
+//               thread), optional SwiGLU forward / backward math, bf16 rounding, 128-bit stores.
+// Tensor memory holds two 128x256 fp32 accumulators (all 512 columns), so the epilogue of tile
+// i overlaps the main loop of tile i+1.
+//
+// Operands may be K-major (the reduction index is contiguous in memory) or MN-major (the row /
+// column index is contiguous); the latter is what dgrad (B = W[e], [K,N] row-major) and wgrad
+// (A = dY^T, B = X, both [tokens, features] row-major) need, so no transposed copies are made.
+// No TMA multicast and no thread-block clusters are used anywhere in this file.
+//
+// Every mbarrier wait is bounded (about one second of %globaltimer); a wait that runs out sets
+// the device status word, raises a CTA-wide abort flag that all other waits poll, and the CTA
+// leaves through the normal teardown (tensor memory is released).
+#include <cuda.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace fmab {
+
+// ---------------------------------------------------------------------------
+// tile shape
+// ---------------------------------------------------------------------------
+constexpr int BM = 128;           // rows of D per tile = TMEM lanes
+constexpr int BN = 256;           // columns of D per tile = TMEM columns per accumulator
+constexpr int BK = 64;            // reduction elements per stage = one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;        // reduction elements per tcgen05.mma (bf16)
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SUPER_M = 16;       // m-tiles walked together so that concurrent CTAs share operand tiles in L2
+constexpr size_t GEMM_SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;
+
+constexpr int EPI_PLAIN = 0;
+constexpr int EPI_SWIGLU_FWD = 1;
+constexpr int EPI_SWIGLU_BWD = 2;
+
+constexpr int MODE_ROWS = 0;     // ragged M: m-tile -> expert through mtile_expert (forward, dgrad)
+constexpr int MODE_WGRAD = 1;    // ragged K: tile = (expert, m-tile, n-tile), k runs over the expert's rows
+constexpr int MODE_GENERAL = 2;  // per-group tensor maps and host-built tables
+
+constexpr int32_t STATUS_GEMM_TIMEOUT = 0x7001;
+
+// Tables of the general mode (host-built, in the caller's workspace).
+struct GroupRec {
+    int32_t m, n, k;      // problem size of the group
+    int32_t first_mtile;  // index of its first m-tile
+    int64_t d_offset;     // element offset of D_g in the packed output
+};
+struct MTileRec {
+    int32_t group;
+    int32_t row0;  // first row of the tile inside the group
+};
+
+struct GemmParams {
+    CUtensorMap map_a;
+    CUtensorMap map_b;
+    const CUtensorMap* group_maps;  // general mode: [2g] = A_g, [2g+1] = B_g
+    const GroupRec* groups;
+    const MTileRec* mtiles;
+    const int32_t* mtile_expert;  // rows mode
+    const int32_t* seg_offsets;   // wgrad mode: [n_seg][E] (+1)
+    __nv_bfloat16* d;             // output (act for SWIGLU_FWD, d_pre for SWIGLU_BWD)
+    __nv_bfloat16* d2;            // SWIGLU_FWD: pre (may be null)
+    const __nv_bfloat16* pre;     // SWIGLU_BWD: saved pre-activations
+    int32_t* status;
+    int64_t ldd;                  // row pitch of d in elements
+    int32_t mode;
+    int32_t n_mtiles;             // m-tiles to walk
+    int32_t n_ntiles;
+    int32_t m_per_group;          // wgrad: rows of D per expert (OUT)
+    int32_t mtiles_per_group;     // wgrad: ceil(OUT / 128)
+    int32_t n_cols;               // columns of D (rows/wgrad modes)
+    int32_t k_len;                // rows mode: reduction length
+    int32_t b_group_stride;       // rows mode: B coordinate step per expert (rows of the stacked weight)
+    int32_t n_groups;             // E
+    int32_t n_seg;                // wgrad: segments per expert
+    int32_t inter;                // SwiGLU: intermediate size I
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t global_timer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the wait was given up (here or by another thread of the CTA).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer() - t0 > 1000000000ull) {  // one second
+            *abort_flag = 1;
+            atomicExch(status, STATUS_GEMM_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tensormap_acquire(const CUtensorMap* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tc_load_32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile.
+//   K-major : rows of 64 bf16 (128 B); 8-row groups 1024 B apart (stride byte offset).
+//   MN-major: rows of 64 MN elements (128 B) per k; 8-k groups 1024 B apart (stride byte offset);
+//             the next 64 MN elements start BK*128 B further (leading byte offset).
+template <bool MN_MAJOR>
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    constexpr uint64_t lbo = MN_MAJOR ? (BK * 128) >> 4 : 1;
+    constexpr uint64_t sbo = 1024 >> 4;
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);  // start address, bits [0,14)
+    d |= lbo << 16;                                           // leading byte offset, bits [16,30)
+    d |= sbo << 32;                                           // stride byte offset, bits [32,46)
+    d |= 1ull << 46;                                          // descriptor version for sm_100
+    d |= 2ull << 61;                                          // layout: 128-byte swizzle
+    return d;
+}
+// Bytes to advance the start address for the next 16 reduction elements.
+template <bool MN_MAJOR>
+__device__ __forceinline__ constexpr uint32_t desc_k_step() { return MN_MAJOR ? UMMA_K * 128 : UMMA_K * 2; }
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ constexpr uint32_t make_instr_desc() {
+    return (1u << 4)                      // accumulator format: fp32
+           | (1u << 7)                    // A format: bf16
+           | (1u << 10)                   // B format: bf16
+           | ((A_MN ? 1u : 0u) << 15)     // A major
+           | ((B_MN ? 1u : 0u) << 16)     // B major
+           | (static_cast<uint32_t>(BN >> 3) << 17)
+           | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// tile decode (identical in all three roles)
+// ---------------------------------------------------------------------------
+struct Tile {
+    const CUtensorMap* map_a;
+    const CUtensorMap* map_b;
+    int32_t group;
+    int32_t a_mn;        // A coordinate along M
+    int32_t b_mn;        // B coordinate along N (of tile column 0)
+    int32_t b_k_base;    // added to B's k coordinate (rows mode, MN-major stacked weights)
+    int32_t n0;          // first D column of the tile
+    int32_t n_valid;     // D columns to store
+    int32_t rows_valid;  // D rows to store
+    int64_t d_row;       // first D row (in units of ldd) ...
+    int64_t d_base;      // ... plus element offset of the group's output (general mode)
+    int64_t ldd;
+};
+
+template <bool B_MN, int EPI>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, Tile& t) {
+    // Walk SUPER_M m-tiles together, n-tile by n-tile.
+    const int per_super = SUPER_M * p.n_ntiles;
+    const int super = tile / per_super;
+    const int m_first = super * SUPER_M;
+    const int m_span = min(SUPER_M, p.n_mtiles - m_first);
+    const int r = tile - super * per_super;
+    const int nt = r / m_span;
+    const int mt = m_first + (r - nt * m_span);
+    constexpr int n_step = (EPI == EPI_SWIGLU_FWD) ? BN / 2 : BN;
+    t.n0 = nt * n_step;
+    t.map_a = &p.map_a;
+    t.map_b = &p.map_b;
+    t.b_k_base = 0;
+    t.d_base = 0;
+    t.ldd = p.ldd;
+    if (p.mode == MODE_ROWS) {
+        const int e = p.mtile_expert[mt];
+        if (e < 0) return false;
+        t.group = e;
+        t.a_mn = mt * BM;
+        t.d_row = static_cast<int64_t>(mt) * BM;
+        t.rows_valid = BM;
+        t.n_valid = min(n_step, p.n_cols - t.n0);
+        if (B_MN) {
+            t.b_mn = t.n0;
+            t.b_k_base = e * p.b_group_stride;
+        } else {
+            t.b_mn = e * p.b_group_stride + t.n0;
+        }
+    } else if (p.mode == MODE_WGRAD) {
+        const int e = mt / p.mtiles_per_group;
+        const int m0 = (mt - e * p.mtiles_per_group) * BM;
+        t.group = e;
+        t.a_mn = m0;
+        t.b_mn = t.n0;
+        t.d_row = static_cast<int64_t>(e) * p.m_per_group + m0;
+        t.rows_valid = min(BM, p.m_per_group - m0);
+        t.n_valid = min(n_step, p.n_cols - t.n0);
+    } else {
+        const MTileRec rec = p.mtiles[mt];
+        const GroupRec g = p.groups[rec.group];
+        if (t.n0 >= g.n) return false;
+        t.group = rec.group;
+        t.map_a = p.group_maps + 2 * rec.group;
+        t.map_b = p.group_maps + 2 * rec.group + 1;
+        t.a_mn = rec.row0;
+        t.b_mn = t.n0;
+        t.d_row = rec.row0;
+        t.d_base = g.d_offset;
+        t.ldd = g.n;
+        t.rows_valid = min(BM, g.m - rec.row0);
+        t.n_valid = min(n_step, g.n - t.n0);
+    }
+    return true;
+}
+
+// k range of segment s of the tile's group: start coordinates in A and B, and length.
+__device__ __forceinline__ void decode_segment(const GemmParams& p, const Tile& t, int s, int& a_k0, int& b_k0, int& len) {
+    if (p.mode == MODE_ROWS) {
+        a_k0 = 0;
+        b_k0 = t.b_k_base;
+        len = p.k_len;
+    } else if (p.mode == MODE_WGRAD) {
+        const int32_t* o = p.seg_offsets + s * p.n_groups + t.group;
+        a_k0 = o[0];
+        b_k0 = o[0];
+        len = o[1] - o[0];
+    } else {
+        a_k0 = 0;
+        b_k0 = 0;
+        len = p.groups[t.group].k;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// epilogue helpers: one thread owns one output row, 32 columns at a time
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float* v, int cols_left) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (q * 8 < cols_left) st_global_16(dst + q * 8, Elem<__nv_bfloat16>::pack(v + q * 8));
+    }
+}
+__device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float* v, int cols_left) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (q * 8 < cols_left) {
+            Elem<__nv_bfloat16>::unpack(ld_global_16(src + q * 8), v + q * 8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[q * 8 + i] = 0.f;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t acc_full_bar[2];
+    __shared__ __align__(8) uint64_t acc_empty_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full_bar[b]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[b]), 4);  // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int* abort_ptr = &abort_flag;
+
+    const int total_tiles = p.n_mtiles * p.n_ntiles;
+    const int n_seg = (p.mode == MODE_WGRAD) ? p.n_seg : 1;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+                Tile t;
+                if (!decode_tile<B_MN, EPI>(p, tile, t)) continue;
+                if (p.mode == MODE_GENERAL) {
+                    tensormap_acquire(t.map_a);
+                    tensormap_acquire(t.map_b);
+                }
+                for (int s = 0; s < n_seg && alive; ++s) {
+                    int a_k0, b_k0, len;
+                    decode_segment(p, t, s, a_k0, b_k0, len);
+                    for (int k = 0; k < len; k += BK) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr, p.status)) {
+                            alive = false;
+                            break;
+                        }
+                        const uint32_t bar = smem_u32(&full_bar[stage]);
+                        const uint32_t sa = ring + stage * STAGE_BYTES;
+                        const uint32_t sb = sa + A_STAGE_BYTES;
+                        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                        if (A_MN) {
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_2d(sa + j * (BK * 128), t.map_a, bar, t.a_mn + 64 * j, a_k0 + k);
+                        } else {
+                            tma_load_2d(sa, t.map_a, bar, a_k0 + k, t.a_mn);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j)
+                                tma_load_2d(sb + j * (BK * 128), t.map_b, bar, t.b_mn + 64 * j, b_k0 + k);
+                        } else if (EPI == EPI_SWIGLU_FWD) {
+                            // up rows n0.. and gate rows I+n0.. of the same expert, 128 each
+                            tma_load_2d(sb, t.map_b, bar, b_k0 + k, t.b_mn);
+                            tma_load_2d(sb + (BN / 2) * (BK * 2), t.map_b, bar, b_k0 + k, t.b_mn + p.inter);
+                        } else {
+                            tma_load_2d(sb, t.map_b, bar, b_k0 + k, t.b_mn);
+                        }
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
+            }
+            if (!alive) {
+                // give copies that are still in flight time to land before the CTA retires
+                for (int i = 0; i < 200; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_instr_desc<A_MN, B_MN>();
+            int stage = 0;
+            uint32_t phase = 0;
+            int buf = 0;
+            uint32_t acc_phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+                Tile t;
+                if (!decode_tile<B_MN, EPI>(p, tile, t)) continue;
+                if (!mbar_wait(smem_u32(&acc_empty_bar[buf]), acc_phase ^ 1u, abort_ptr, p.status)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                uint32_t accumulate = 0;
+                for (int s = 0; s < n_seg && alive; ++s) {
+                    int a_k0, b_k0, len;
+                    decode_segment(p, t, s, a_k0, b_k0, len);
+                    for (int k = 0; k < len; k += BK) {
+                        if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_ptr, p.status)) {
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sa = ring + stage * STAGE_BYTES;
+                        const uint32_t sb = sa + A_STAGE_BYTES;
+                        const uint64_t a_desc = make_smem_desc<A_MN>(sa);
+                        const uint64_t b_desc = make_smem_desc<B_MN>(sb);
+#pragma unroll
+                        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                            tc_mma(d_tmem, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
+                                   b_desc + ((ks * desc_k_step<B_MN>()) >> 4), idesc, accumulate);
+                            accumulate = 1;
+                        }
+                        tc_commit(smem_u32(&empty_bar[stage]));  // stage is free once these MMAs have read it
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
+                if (!alive) break;
+                if (accumulate) tc_commit(smem_u32(&acc_full_bar[buf]));
+                else mbar_arrive(smem_u32(&acc_full_bar[buf]));  // empty reduction: the epilogue writes zeros
+                if (++buf == 2) {
+                    buf = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are visible to this warp
+        const int row_in_tile = quad * 32 + lane;
+        int buf = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            Tile t;
+            if (!decode_tile<B_MN, EPI>(p, tile, t)) continue;
+            // Does this tile have any reduction work?  (Same test as the MMA issuer's.)
+            bool any_k = false;
+            for (int s = 0; s < n_seg; ++s) {
+                int a_k0, b_k0, len;
+                decode_segment(p, t, s, a_k0, b_k0, len);
+                any_k |= len > 0;
+            }
+            if (!mbar_wait(smem_u32(&acc_full_bar[buf]), acc_phase, abort_ptr, p.status)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quad * 32) << 16);
+            const bool row_ok = row_in_tile < t.rows_valid;
+            const int64_t grow = t.d_row + row_in_tile;
+
+            if (EPI == EPI_PLAIN) {
+                __nv_bfloat16* drow = p.d + t.d_base + grow * t.ldd + t.n0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int cols_left = t.n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    float v[32];
+                    if (any_k) {
+                        tc_load_32(taddr + c * 32, v);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                    }
+                    if (row_ok) store_row32_bf16(drow + c * 32, v, cols_left);
+                }
+            } else if (EPI == EPI_SWIGLU_FWD) {
+                // accumulator columns [0,128) = up, [128,256) = gate, for act columns n0..n0+127
+                __nv_bfloat16* arow = p.d + grow * p.ldd + t.n0;
+                __nv_bfloat16* prow = p.d2 ? p.d2 + grow * (2 * static_cast<int64_t>(p.inter)) + t.n0 : nullptr;
+#pragma unroll 1
+                for (int c = 0; c < BN / 64; ++c) {
+                    const int cols_left = t.n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    float u[32], g[32];
+                    tc_load_32(taddr + c * 32, u);
+                    tc_load_32(taddr + BN / 2 + c * 32, g);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        u[i] = round_bf16(u[i]);
+                        g[i] = round_bf16(g[i]);
+                    }
+                    if (row_ok && prow) {
+                        store_row32_bf16(prow + c * 32, u, cols_left);
+                        store_row32_bf16(prow + p.inter + c * 32, g, cols_left);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped(g[i]);
+                    if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
+                }
+            } else {
+                // d_act tile -> d_up, d_gate using the saved pre-activations
+                const __nv_bfloat16* prow = p.pre + grow * (2 * static_cast<int64_t>(p.inter)) + t.n0;
+                __nv_bfloat16* drow = p.d + grow * (2 * static_cast<int64_t>(p.inter)) + t.n0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int cols_left = t.n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    float da[32], u[32], g[32];
+                    tc_load_32(taddr + c * 32, da);
+                    if (row_ok) {
+                        load_row32_bf16(prow + c * 32, u, cols_left);
+                        load_row32_bf16(prow + p.inter + c * 32, g, cols_left);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float d = round_bf16(da[i]);
+                            const float s = sigmoid_clamped(g[i]);
+                            const float silu = g[i] * s;
+                            da[i] = d * silu;                           // d_up
+                            g[i] = d * u[i] * (s + silu * (1.f - s));   // d_gate
+                        }
+                        store_row32_bf16(drow + c * 32, da, cols_left);
+                        store_row32_bf16(drow + p.inter + c * 32, g, cols_left);
+                    }
+                }
+            }
+            // all of this warp's TMEM reads are complete (tcgen05.wait::ld inside tc_load_32)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buf]));
+            if (++buf == 2) {
+                buf = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps and launches
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor [outer, inner] with row pitch `pitch` elements, box [box_outer, box_inner], 128-byte swizzle.
+static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
+                     uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    FMAB_REQUIRE(fn != nullptr, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
+    FMAB_REQUIRE(aligned16(base), FMA_B200_ERR_BAD_ARG, "GEMM operand is not 16-byte aligned");
+    FMAB_REQUIRE((pitch * 2) % 16 == 0, FMA_B200_ERR_BAD_ARG, "row pitch %llu elements is not a multiple of 8",
+                 (unsigned long long)pitch);
+    FMAB_REQUIRE(inner >= 1 && outer >= 1, FMA_B200_ERR_BAD_ARG, "empty tensor for a tensor map");
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {pitch * 2};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FMAB_REQUIRE(r == CUDA_SUCCESS, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FMA_B200_OK;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const GemmParams& p, cudaStream_t s) {
+    static bool configured = false;
+    auto kernel = gemm_tc_kernel<A_MN, B_MN, EPI>;
+    if (!configured) {
+        FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
+        configured = true;
+    }
+    const int64_t total = static_cast<int64_t>(p.n_mtiles) * p.n_ntiles;
+    if (total <= 0) return FMA_B200_OK;
+    FMAB_REQUIRE(total < (1LL << 31), FMA_B200_ERR_BAD_ARG, "too many tiles");
+    const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
+    kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(p);
+    return check_launch("grouped GEMM (tcgen05)");
+}
+
+static int fill_common(GemmParams& p) {
+    memset(&p, 0, sizeof(p));
+    p.status = device_status_ptr();
+    FMAB_REQUIRE(p.status != nullptr, FMA_B200_ERR_LAUNCH, "no device status word");
+    p.n_seg = 1;
+    return FMA_B200_OK;
+}
+
+int tc_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
+               const int32_t* mtile_expert, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, BN)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.d = static_cast<__nv_bfloat16*>(Y);
+    p.ldd = OUT;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (OUT + BN - 1) / BN;
+    p.n_cols = OUT;
+    p.k_len = IN;
+    p.b_group_stride = OUT;
+    p.n_groups = E;
+    return launch_gemm<false, false, EPI_PLAIN>(p, s);
+}
+
+int tc_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
+                      const int32_t* mtile_expert, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * 2 * I, IN, BK, BN / 2)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.d = static_cast<__nv_bfloat16*>(act);
+    p.d2 = static_cast<__nv_bfloat16*>(pre);
+    p.ldd = I;
+    p.inter = I;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (I + BN / 2 - 1) / (BN / 2);
+    p.n_cols = I;
+    p.k_len = IN;
+    p.b_group_stride = 2 * I;
+    p.n_groups = E;
+    return launch_gemm<false, false, EPI_SWIGLU_FWD>(p, s);
+}
+
+int tc_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
+             const int32_t* mtile_expert, bool swiglu, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
+    // W[e] is [OUT, IN] row-major = the [K, N] operand with N contiguous: MN-major B, boxes of 64 columns x BK rows
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.d = static_cast<__nv_bfloat16*>(dX);
+    p.pre = static_cast<const __nv_bfloat16*>(pre);
+    p.ldd = swiglu ? 2 * static_cast<int64_t>(IN) : IN;
+    p.inter = IN;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (IN + BN - 1) / BN;
+    p.n_cols = IN;
+    p.k_len = OUT;
+    p.b_group_stride = OUT;
+    p.n_groups = E;
+    if (swiglu) return launch_gemm<false, true, EPI_SWIGLU_BWD>(p, s);
+    return launch_gemm<false, true, EPI_PLAIN>(p, s);
+}
+
+int tc_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
+             const int32_t* seg_offsets, int n_seg, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_common(p)) return rc;
+    // both operands are [tokens, features] row-major: the token (reduction) index is the outer dimension
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, 64, BK)) return rc;
+    if (int rc = encode_2d(&p.map_b, X, IN, rows_cap, IN, 64, BK)) return rc;
+    p.mode = MODE_WGRAD;
+    p.seg_offsets = seg_offsets;
+    p.n_seg = n_seg;
+    p.d = static_cast<__nv_bfloat16*>(dW);
+    p.ldd = IN;
+    p.m_per_group = OUT;
+    p.mtiles_per_group = (OUT + BM - 1) / BM;
+    p.n_mtiles = E * p.mtiles_per_group;
+    p.n_ntiles = (IN + BN - 1) / BN;
+    p.n_cols = IN;
+    p.n_groups = E;
+    return launch_gemm<true, true, EPI_PLAIN>(p, s);
+}
+
+struct GeneralLayout {
+    int64_t groups_off, mtiles_off, maps_off, total;
+};
+static GeneralLayout general_layout(int n_groups, int64_t total_mtiles) {
+    GeneralLayout l;
+    l.maps_off = 0;  // tensor maps first: they need 64-byte alignment (the workspace must be 128-byte aligned)
+    l.groups_off = static_cast<int64_t>(n_groups) * 2 * sizeof(CUtensorMap);
+    l.mtiles_off = l.groups_off + ((static_cast<int64_t>(n_groups) * sizeof(GroupRec) + 127) / 128) * 128;
+    l.total = l.mtiles_off + ((total_mtiles * static_cast<int64_t>(sizeof(MTileRec)) + 127) / 128) * 128;
+    return l;
+}
+
+int tc_general(const void* A, const void* B, void* D, const uint32_t* M, const uint32_t* N, const uint32_t* K,
+               int n_groups, bool a_t, bool b_t, void* workspace, int64_t workspace_bytes, cudaStream_t s) {
+    FMAB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 127u) == 0, FMA_B200_ERR_BAD_ARG,
+                 "grouped_gemm workspace must be 128-byte aligned");
+    int64_t total_mtiles = 0;
+    uint32_t max_n = 0;
+    for (int g = 0; g < n_groups; ++g) {
+        total_mtiles += (M[g] + BM - 1) / BM;
+        if (N[g] > max_n) max_n = N[g];
+    }
+    const GeneralLayout lay = general_layout(n_groups, total_mtiles);
+    FMAB_REQUIRE(workspace_bytes >= lay.total, FMA_B200_ERR_WORKSPACE, "grouped_gemm workspace: %lld < %lld bytes",
+                 (long long)workspace_bytes, (long long)lay.total);
+    if (total_mtiles == 0 || max_n == 0) return FMA_B200_OK;
+    std::vector<uint8_t> host(static_cast<size_t>(lay.total), 0);
+    CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(host.data() + lay.maps_off);
+    GroupRec* groups = reinterpret_cast<GroupRec*>(host.data() + lay.groups_off);
+    MTileRec* mtiles = reinterpret_cast<MTileRec*>(host.data() + lay.mtiles_off);
+    const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(A);
+    const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(B);
+    int64_t a_off = 0, b_off = 0, d_off = 0;
+    int32_t mt = 0;
+    for (int g = 0; g < n_groups; ++g) {
+        const uint64_t m = M[g], n = N[g], k = K[g];
+        FMAB_REQUIRE(m < (1u << 31) && n < (1u << 31) && k < (1u << 31), FMA_B200_ERR_BAD_ARG, "group %d too large", g);
+        groups[g].m = (int32_t)m;
+        groups[g].n = (int32_t)n;
+        groups[g].k = (int32_t)k;
+        groups[g].first_mtile = mt;
+        groups[g].d_offset = d_off;
+        FMAB_REQUIRE(n % 8 == 0, FMA_B200_ERR_BAD_ARG, "group %d: N=%llu must be a multiple of 8", g, (unsigned long long)n);
+        if (m > 0 && n > 0 && k > 0) {
+            int rc;
+            if (a_t) rc = encode_2d(&maps[2 * g], a + a_off, m, k, m, 64, BK);       // [K, M], M contiguous
+            else rc = encode_2d(&maps[2 * g], a + a_off, k, m, k, BK, BM);           // [M, K], K contiguous
+            if (rc) return rc;
+            if (b_t) rc = encode_2d(&maps[2 * g + 1], b + b_off, k, n, k, BK, BN);   // [N, K], K contiguous
+            else rc = encode_2d(&maps[2 * g + 1], b + b_off, n, k, n, 64, BK);       // [K, N], N contiguous
+            if (rc) return rc;
+        }
+        for (uint64_t r = 0; r < m; r += BM) {
+            mtiles[mt].group = g;
+            mtiles[mt].row0 = (int32_t)r;
+            ++mt;
+        }
+        a_off += m * k;
+        b_off += k * n;
+        d_off += m * n;
+    }
+    FMAB_CUDA(cudaMemcpyAsync(workspace, host.data(), static_cast<size_t>(lay.total), cudaMemcpyHostToDevice, s));
+    GemmParams p;
+    if (int rc = fill_common(p)) return rc;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    p.mode = MODE_GENERAL;
+    p.group_maps = reinterpret_cast<const CUtensorMap*>(ws + lay.maps_off);
+    p.groups = reinterpret_cast<const GroupRec*>(ws + lay.groups_off);
+    p.mtiles = reinterpret_cast<const MTileRec*>(ws + lay.mtiles_off);
+    p.d = static_cast<__nv_bfloat16*>(D);
+    p.n_mtiles = (int)total_mtiles;
+    p.n_ntiles = (int)((max_n + BN - 1) / BN);
+    p.n_groups = n_groups;
+    if (!a_t && b_t) return launch_gemm<false, false, EPI_PLAIN>(p, s);
+    if (!a_t && !b_t) return launch_gemm<false, true, EPI_PLAIN>(p, s);
+    if (a_t && b_t) return launch_gemm<true, false, EPI_PLAIN>(p, s);
+    return launch_gemm<true, true, EPI_PLAIN>(p, s);
+}
+
+int64_t tc_general_workspace_bytes(int n_groups, int64_t total_mtiles) {
+    return general_layout(n_groups, total_mtiles).total;
+}
+
+}  // namespace fmab

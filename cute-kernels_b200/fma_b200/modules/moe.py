@@ -1,0 +1,271 @@
+"""`MoE` and `Experts` with the reference's constructor, forward signature, parameter names and
+state_dict keys (fma/modules/moe/__init__.py:17-124, :127-298), running on hand-written sm_100a
+kernels only.
+
+Data flow of `MoE.forward` (T tokens, R = T*k routed rows):
+    logits = gate(x)                                  nn.Linear, kept as a replaceable module
+    w, sel = top-k + softmax kernel                   [T,k]
+    maps   = stable counting sort of sel              expert segments padded to 128-row tiles
+    xg     = scatter(x)                               [rows_cap, H], padding rows zero
+    pre, a = up-projection GEMM (+ SwiGLU epilogue)   tcgen05 for bf16, FFMA for f32
+    out    = down-projection GEMM
+    y      = sum_j w[t,j] * out[row(t,j)]             weighted combine
+Backward mirrors it with dgrad / wgrad GEMMs (SwiGLU backward in the dgrad epilogue).
+"""
+
+from __future__ import annotations
+
+import functools
+from typing import Callable
+
+import torch
+import torch.nn as nn
+
+from .. import _native
+from ..kernel_backend import KernelBackend
+from ..ops.swiglu import swiglu_packed
+from . import _kernels as K
+
+
+class _RouterTopK(torch.autograd.Function):
+    """(weights, selected) = softmax(topk(logits)); backward scatters into d_logits."""
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, k: int):
+        weights, selected = K.router_topk_softmax(logits, k)
+        ctx.save_for_backward(weights, selected)
+        ctx.num_experts = logits.size(1)
+        ctx.mark_non_differentiable(selected)
+        return weights, selected
+
+    @staticmethod
+    def backward(ctx, d_weights, _d_selected):
+        weights, selected = ctx.saved_tensors
+        return K.router_topk_softmax_backward(weights, d_weights, selected, ctx.num_experts), None
+
+
+class _Scatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, maps: K.RowMaps):
+        ctx.maps = maps
+        ctx.T = x.size(0)
+        return K.scatter(x.contiguous(), maps)
+
+    @staticmethod
+    def backward(ctx, d_grouped):
+        return K.scatter_backward(d_grouped.contiguous(), ctx.maps, ctx.T), None
+
+
+class _ExpertLinear(torch.autograd.Function):
+    """Y[p] = X[p] . W[e(p)]^T over the grouped layout (Experts.cuda_forward of the reference)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, maps: K.RowMaps):
+        x = x.contiguous()
+        weight = weight.contiguous()
+        ctx.save_for_backward(x, weight)
+        ctx.maps = maps
+        return K.gemm_forward(x, weight, maps.mtile_expert)
+
+    @staticmethod
+    def backward(ctx, d_y):
+        x, weight = ctx.saved_tensors
+        maps = ctx.maps
+        d_y = d_y.contiguous()
+        d_x = K.gemm_dgrad(d_y, weight, maps.mtile_expert) if ctx.needs_input_grad[0] else None
+        d_w = K.gemm_wgrad(d_y, x, weight.size(0), maps.pad_offsets) if ctx.needs_input_grad[1] else None
+        return d_x, d_w, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, expert_out, weights, maps: K.RowMaps, T: int):
+        expert_out = expert_out.contiguous()
+        weights = weights.contiguous()
+        ctx.save_for_backward(expert_out, weights)
+        ctx.maps = maps
+        return K.combine(expert_out, weights, maps, T)
+
+    @staticmethod
+    def backward(ctx, dy):
+        expert_out, weights = ctx.saved_tensors
+        d_out, d_w = K.combine_backward(dy.contiguous(), expert_out, weights, ctx.maps, ctx.needs_input_grad[1])
+        return d_out, d_w, None, None
+
+
+class _FusedSwigluExperts(torch.autograd.Function):
+    """scatter -> up projection with SwiGLU epilogue -> down projection -> weighted combine, and the
+    matching backward, as one autograd node (no intermediate autograd bookkeeping, `pre` and `act`
+    are produced by one kernel, d_pre by one kernel)."""
+
+    @staticmethod
+    def forward(ctx, x, weights, w_fc, w_proj, maps: K.RowMaps):
+        x = x.contiguous()
+        weights = weights.contiguous()
+        w_fc = w_fc.contiguous()
+        w_proj = w_proj.contiguous()
+        T = x.size(0)
+        xg = K.scatter(x, maps)
+        pre, act = K.gemm_forward_swiglu(xg, w_fc, maps.mtile_expert, keep_pre=True)
+        out = K.gemm_forward(act, w_proj, maps.mtile_expert)
+        y = K.combine(out, weights, maps, T)
+        ctx.save_for_backward(xg, pre, act, out, weights, w_fc, w_proj)
+        ctx.maps = maps
+        ctx.T = T
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, pre, act, out, weights, w_fc, w_proj = ctx.saved_tensors
+        maps = ctx.maps
+        E = w_fc.size(0)
+        need_x, need_w, need_fc, need_proj = ctx.needs_input_grad[:4]
+        d_out, d_w = K.combine_backward(dy.contiguous(), out, weights, maps, need_w)
+        d_w_proj = K.gemm_wgrad(d_out, act, E, maps.pad_offsets) if need_proj else None
+        d_x = d_w_fc = None
+        if need_x or need_fc:
+            d_pre = K.gemm_dgrad_swiglu(d_out, w_proj, pre, maps.mtile_expert)
+            if need_fc:
+                d_w_fc = K.gemm_wgrad(d_pre, xg, E, maps.pad_offsets)
+            if need_x:
+                d_xg = K.gemm_dgrad(d_pre, w_fc, maps.mtile_expert)
+                d_x = K.scatter_backward(d_xg, maps, ctx.T)
+        return d_x, d_w, d_w_fc, d_w_proj, None
+
+
+def _is_swiglu_packed(fn: Callable) -> bool:
+    """True if `fn` is this package's swiglu_packed (possibly wrapped in functools.partial with
+    backend keywords only), so that it can run inside the GEMM epilogue."""
+    if fn is swiglu_packed:
+        return True
+    if isinstance(fn, functools.partial) and fn.func is swiglu_packed and not fn.args:
+        return set(fn.keywords) <= {"kernel_backend_forward", "kernel_backend_backward"}
+    return bool(getattr(fn, "_fma_b200_is_swiglu_packed", False))
+
+
+class Experts(nn.Module):
+    def __init__(
+        self, num_experts: int, in_features: int, out_features: int, add_bias: bool = True, std: float | None = None
+    ) -> None:
+        super().__init__()
+
+        self.weight = nn.Parameter(torch.empty(num_experts, out_features, in_features))
+
+        self.bias = None
+        if add_bias:
+            self.bias = nn.Parameter(torch.empty(num_experts, out_features))
+
+        self.std = std
+
+        self.num_experts = num_experts
+        self.in_features = in_features
+        self.out_features = out_features
+
+        self.register_buffer("N_array", torch.empty((num_experts,), dtype=torch.uint32))
+        self.register_buffer("K_array", torch.empty((num_experts,), dtype=torch.uint32))
+
+        self.reset_parameters()
+
+    def grouped_forward(self, input: torch.Tensor, maps: K.RowMaps) -> torch.Tensor:
+        """Y = X . W[e]^T over the grouped layout (rows of expert e in maps.pad_offsets[e:e+2])."""
+        if self.bias is not None:
+            raise NotImplementedError("Experts with add_bias=True are not supported by the B200 kernels yet")
+        return _ExpertLinear.apply(input, self.weight, maps)
+
+    def extra_repr(self):
+        return "num_experts={}, in_features={}, out_features={}".format(
+            self.num_experts, self.in_features, self.out_features
+        )
+
+    @torch.no_grad()
+    def reset_parameters(self) -> None:
+        nn.init.normal_(self.weight, mean=0, std=self.std)
+        if hasattr(self, "bias") and self.bias is not None:
+            self.bias.zero_()
+
+        self.N_array.fill_(self.out_features)
+        self.K_array.fill_(self.in_features)
+
+
+class MoE(nn.Module):
+    def __init__(
+        self,
+        num_experts: int,
+        num_experts_per_tok: int,
+        hidden_size: int,
+        intermediate_size: int,
+        activation_function: Callable,
+        is_glu: bool,
+        add_bias: bool,
+        std: float,
+    ) -> None:
+        super().__init__()
+
+        self.num_experts = num_experts
+        self.top_k = num_experts_per_tok
+
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.is_glu = is_glu
+
+        self.gate = nn.Linear(in_features=self.hidden_size, out_features=num_experts, bias=False)
+
+        self.c_fc = Experts(
+            num_experts=num_experts,
+            in_features=self.hidden_size,
+            out_features=2 * self.intermediate_size if is_glu else self.intermediate_size,
+            add_bias=add_bias,
+            std=std,
+        )
+
+        self.act = activation_function
+
+        self.c_proj = Experts(
+            num_experts=num_experts,
+            in_features=self.intermediate_size,
+            out_features=self.hidden_size,
+            add_bias=add_bias,
+            std=std,
+        )
+
+    def forward(
+        self, hidden_states: torch.Tensor, kernel_backend: KernelBackend = KernelBackend.triton
+    ) -> tuple[torch.Tensor, torch.Tensor]:
+        """Returns (output with the shape of `hidden_states`, router_logits [T, num_experts]).
+        `kernel_backend` is accepted for compatibility; every value runs the same CUDA kernels."""
+        if not isinstance(kernel_backend, KernelBackend):
+            raise ValueError(f"unexpected kernel_backend ({kernel_backend})")
+        _native.require_cuda(hidden_states)
+        original_shape = hidden_states.shape
+        hidden_states = hidden_states.reshape(-1, self.hidden_size)
+
+        with torch.cuda.device(hidden_states.device):
+            router_logits, router_weights, selected_experts = self._compute_routing_weights(hidden_states)
+            hidden_states = self._compute_experts(hidden_states, router_weights, selected_experts)
+
+        return hidden_states.view(original_shape), router_logits
+
+    def _compute_routing_weights(self, hidden_states: torch.Tensor):
+        router_logits = self.gate(hidden_states)
+        router_weights, selected_experts = _RouterTopK.apply(router_logits, self.top_k)
+        return router_logits, router_weights, selected_experts
+
+    def _compute_experts(
+        self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor
+    ) -> torch.Tensor:
+        T = hidden_states.size(0)
+        with torch.no_grad():
+            maps = K.moe_sort(selected_experts, self.num_experts)
+        self.last_row_maps = maps  # expert_count etc. for callers that log load balance
+
+        fused = (
+            self.is_glu and _is_swiglu_packed(self.act) and self.c_fc.bias is None and self.c_proj.bias is None
+        )
+        if fused:
+            return _FusedSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps)
+
+        grouped = _Scatter.apply(hidden_states, maps)
+        grouped = self.c_fc.grouped_forward(grouped, maps)
+        grouped = self.act(grouped)
+        grouped = self.c_proj.grouped_forward(grouped, maps)
+        return _Combine.apply(grouped, router_weights, maps, T)

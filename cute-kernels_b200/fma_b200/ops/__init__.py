@@ -1,0 +1,3 @@
+from .continuous_count import continuous_count
+from .grouped_gemm import grouped_gemm
+from .swiglu import swiglu, swiglu_packed
