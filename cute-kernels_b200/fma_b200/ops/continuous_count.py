@@ -38,6 +38,8 @@ def continuous_count(
     assert x.dtype in [torch.int32, torch.long]
     _native.require_cuda(x)
     x = x.contiguous()
+    if x.data_ptr() % 16 != 0:  # the kernel reads 128-bit vectors
+        x = x.clone()
 
     output = torch.empty(size, dtype=torch.uint32, device=x.device)
     ws = _workspace(x.device, size)

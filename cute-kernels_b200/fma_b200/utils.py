@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import functools
 import random
 from typing import Any, Callable
 
@@ -17,11 +18,10 @@ def _make_contiguous(x: Any) -> Any:
 def ensure_contiguous(func: Callable) -> Callable:
     """Decorator: every tensor argument is made contiguous before the call."""
 
+    @functools.wraps(func)
     def inner(*args, **kwargs):
         return func(*tree_map(_make_contiguous, args), **tree_map(_make_contiguous, kwargs))
 
-    inner.__name__ = getattr(func, "__name__", "inner")
-    inner.__doc__ = func.__doc__
     return inner
 
 
