@@ -1,0 +1,546 @@
+"""Benchmark of the MoE-layer hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).  A step is one forward +
+backward of the layer over one batch of seeded synthetic tokens.  Rank 0 prints ONE JSON line.
+
+Workloads (all synthetic, shapes from the benchmark specification):
+  ep_c5          per GPU T=65536, H=4096, E=128 experts in total sharded over the N ranks, top-8,
+                 I=1536, bf16, uniform router.  Default at every N (at N=1 all 128 experts are local),
+                 so the 1/2/4/8-GPU series is one weak-scaling series.
+  mixtral_c3     T=16384, H=4096, E=8, top-2, I=14336, bf16 (single GPU)
+  finegrained_c4 T=32768, H=2048, E=128, top-8, I=768, bf16, Zipf(1.0) expert load (single GPU)
+  small_c1       T=4096, H=1024, E=8, top-2, I=512, fp32 (single GPU)
+  count_c2       continuous_count alone: 2^24 int32 ids, 128 bins, uniform or Zipf(1.1)
+
+Keys of the JSON line beyond the common ones:
+  value      tokens/s of the whole job with inputs resident in HBM (device-timed, max over ranks)
+  e2e        the same through the public API with HOST (pinned) x and dy: H2D copies of both and D2H
+             copies of y and dx are inside the timed region
+  roofline   for the dominant kernel (the tcgen05 grouped GEMM: all six launches of a step), achieved
+             TFLOP/s from CUDA events around the launches inside the timed region
+  kernels    per entry point: calls per step, ms per step, achieved GB/s or TFLOP/s, fraction of peak
+  cpu_baseline  the CPU oracle (numpy port of the reference's torch backend) timed on this host on a
+             bounded sample of the same workload (N=1, rank 0 only)
+
+`--impl reference` times that CPU port on the same workload description instead of the CUDA path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT / "cute-kernels_b200", ROOT):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+WORKLOADS = {
+    "ep_c5": dict(T=65536, H=4096, E=128, k=8, I=1536, dtype="bf16", router="uniform"),
+    "mixtral_c3": dict(T=16384, H=4096, E=8, k=2, I=14336, dtype="bf16", router="uniform"),
+    "finegrained_c4": dict(T=32768, H=2048, E=128, k=8, I=768, dtype="bf16", router="zipf"),
+    "small_c1": dict(T=4096, H=1024, E=8, k=2, I=512, dtype="f32", router="uniform"),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=self.file, stderr=subprocess.DEVNULL)  # fmt: skip
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict | None:
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        rows = [line.split(", ") for line in Path(self.file.name).read_text().strip().splitlines() if line.strip()]
+        os.unlink(self.file.name)
+        rows = [r for r in rows if len(r) >= 9]
+        if not rows:
+            return None
+        sm = sorted(float(r[1]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "samples": len(rows), "power_w_max": max(float(r[3]) for r in rows)}  # fmt: skip
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic data
+# ---------------------------------------------------------------------------------------------
+def make_layer(cfg: dict, rank: int, world: int, device: torch.device):
+    """The layer with seeded N(0, 0.02) weights.  Expert e is drawn from seed 1000+e, so a sharded run
+    holds exactly the experts of the unsharded one."""
+    import fma_b200
+
+    dtype = torch.bfloat16 if cfg["dtype"] == "bf16" else torch.float32
+    E, k, H, I = cfg["E"], cfg["k"], cfg["H"], cfg["I"]
+    with torch.device("meta"):
+        cls = fma_b200.ExpertParallelMoE if world > 1 else fma_b200.MoE
+        layer = cls(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02)
+    layer = layer.to_empty(device=device).to(dtype)
+    gen = torch.Generator(device=device)
+    first = rank * (E // world) if world > 1 else 0
+    with torch.no_grad():
+        for j in range(layer.c_fc.weight.size(0)):
+            gen.manual_seed(1000 + first + j)
+            layer.c_fc.weight[j].copy_(torch.randn(layer.c_fc.weight.shape[1:], generator=gen, device=device) * 0.02)
+            layer.c_proj.weight[j].copy_(torch.randn(layer.c_proj.weight.shape[1:], generator=gen, device=device) * 0.02)
+        gen.manual_seed(7)
+        layer.gate.weight.copy_(torch.randn(E, H, generator=gen, device=device) * 0.02)
+        for m in (layer.c_fc, layer.c_proj):
+            m.N_array.fill_(m.out_features)
+            m.K_array.fill_(m.in_features)
+        if cfg["router"] == "zipf":
+            # per-expert bias so that expert load follows Zipf(1.0) over a seeded permutation
+            gate = torch.nn.Linear(H, E, bias=True, device=device, dtype=dtype)
+            p = 1.0 / torch.arange(1, E + 1, dtype=torch.float64)
+            perm = torch.randperm(E, generator=torch.Generator().manual_seed(3))
+            gate.weight.copy_(layer.gate.weight)
+            gate.bias.copy_(torch.log(p / p.sum())[perm].to(dtype))
+            layer.gate = gate
+    return layer, dtype
+
+
+def make_inputs(cfg: dict, rank: int, device: torch.device, dtype):
+    gen = torch.Generator(device=device)
+    gen.manual_seed(100 + rank)
+    x = torch.randn(cfg["T"], cfg["H"], generator=gen, device=device).to(dtype)
+    dy = torch.randn(cfg["T"], cfg["H"], generator=gen, device=device).to(dtype)
+    return x, dy
+
+
+def layer_step(layer, x, dy):
+    for p in layer.parameters():
+        p.grad = None
+    x.grad = None
+    y, _ = layer(x)
+    y.backward(dy)
+    return y
+
+
+# ---------------------------------------------------------------------------------------------
+# algorithmic work (what roofline figures are computed from)
+# ---------------------------------------------------------------------------------------------
+def algorithmic_work(cfg: dict) -> dict:
+    T, H, E, k, I = cfg["T"], cfg["H"], cfg["E"], cfg["k"], cfg["I"]
+    s = 2 if cfg["dtype"] == "bf16" else 4
+    R = T * k
+    gemm = {  # FLOPs = 2*M*N*K over token rows only (no padding counted)
+        "fma_b200_moe_gemm_forward_swiglu": 4 * R * H * I,
+        "fma_b200_moe_gemm_forward": 2 * R * H * I + (4 * R * H * I if cfg["dtype"] == "f32" else 0),
+        "fma_b200_moe_gemm_dgrad_swiglu": 2 * R * H * I,
+        "fma_b200_moe_gemm_dgrad": 4 * R * H * I + (2 * R * H * I if cfg["dtype"] == "f32" else 0),
+        "fma_b200_moe_gemm_wgrad": 6 * R * H * I,
+    }
+    hbm = {  # bytes
+        "fma_b200_moe_scatter": (T + R) * H * s + R * 8,
+        "fma_b200_moe_combine": (R + T) * H * s + R * s,
+        "fma_b200_moe_combine_backward": (T + 2 * R) * H * s + R * s,
+        "fma_b200_moe_scatter_backward": (R + T) * H * s,
+        "fma_b200_moe_sort": 2 * R * 8 + 2 * R * 4,
+        "fma_b200_router_topk_softmax": T * E * s + T * k * (s + 8),
+        "fma_b200_router_topk_softmax_backward": T * E * s + T * k * (2 * s + 8),
+    }
+    return {"gemm_flops": gemm, "hbm_bytes": hbm, "gemm_flops_total": 18 * R * H * I}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline (the oracle port), bounded sample
+# ---------------------------------------------------------------------------------------------
+def cpu_sample_tokens(cfg: dict) -> int:
+    """Tokens of the bounded CPU sample: about 0.5 TFLOP of expert GEMMs, at least one row per expert
+    on average, never more than the workload itself."""
+    per_token = 18 * cfg["k"] * cfg["H"] * cfg["I"]
+    t = int(0.5e12 / per_token)
+    t = max(t, cfg["E"] // cfg["k"], 64)
+    return min(t, cfg["T"])
+
+
+def cpu_oracle_pass(cfg: dict, weights: dict, seed: int) -> tuple[float, int]:
+    """One forward+backward of the oracle on a seeded sample; returns (seconds, tokens)."""
+    from oracle import moe_oracle as O
+
+    t_s = cpu_sample_tokens(cfg)
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((t_s, cfg["H"]), dtype=np.float32)
+    dy = rng.standard_normal((t_s, cfg["H"]), dtype=np.float32)
+    if cfg["dtype"] == "bf16":
+        x, dy = O.bf16_round(x), O.bf16_round(dy)
+    t0 = time.perf_counter()
+    fwd = O.moe_forward(x, weights["w_gate"], weights["w_fc"], weights["w_proj"], cfg["k"], cfg["dtype"],
+                        gate_bias=weights.get("gate_bias"))
+    O.moe_backward(fwd, dy, keep_weight_grads=False)
+    return time.perf_counter() - t0, t_s
+
+
+def host_weights_from_layer(layer) -> dict:
+    f = lambda t: t.detach().float().cpu().numpy()  # noqa: E731
+    w = {"w_gate": f(layer.gate.weight), "w_fc": f(layer.c_fc.weight), "w_proj": f(layer.c_proj.weight)}
+    if getattr(layer.gate, "bias", None) is not None:
+        w["gate_bias"] = f(layer.gate.bias)
+    return w
+
+
+def host_weights_seeded(cfg: dict) -> dict:
+    """Weights for the reference arm when no GPU copy exists: seeded N(0, 0.02), bf16-rounded if needed."""
+    from oracle import moe_oracle as O
+
+    rng = np.random.default_rng(1000)
+    E, H, I = cfg["E"], cfg["H"], cfg["I"]
+    w = {"w_gate": rng.standard_normal((E, H), dtype=np.float32) * 0.02,
+         "w_fc": rng.standard_normal((E, 2 * I, H), dtype=np.float32) * 0.02,
+         "w_proj": rng.standard_normal((E, H, I), dtype=np.float32) * 0.02}  # fmt: skip
+    if cfg["dtype"] == "bf16":
+        w = {n: O.bf16_round(a) for n, a in w.items()}
+    if cfg["router"] == "zipf":
+        p = 1.0 / np.arange(1, E + 1)
+        w["gate_bias"] = np.log(p / p.sum())[np.random.default_rng(3).permutation(E)].astype(np.float32)
+    return w
+
+
+def cpu_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+
+        n = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
+        if n:
+            return int(max(n))
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm
+# ---------------------------------------------------------------------------------------------
+def run_reference(args, cfg: dict, name: str) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    weights = host_weights_seeded(cfg)
+    for i in range(args.warmup):
+        cpu_oracle_pass(cfg, weights, seed=i)
+    secs, toks = 0.0, 0
+    for i in range(args.steps):
+        s, t = cpu_oracle_pass(cfg, weights, seed=100 + i)
+        secs += s
+        toks += t
+    value = toks / secs
+    line = {
+        "impl": "reference", "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+        "config": {"workload": name, **{k: cfg[k] for k in ("T", "H", "E", "k", "I")},
+                   "note": "CPU port of the reference torch backend; each step is a bounded sample of the workload"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+                         "sample": f"{toks // args.steps} tokens per step, all {cfg['E']} experts, numpy fp32 matmul "
+                                   f"with {cfg['dtype']} rounding points"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# continuous_count workload
+# ---------------------------------------------------------------------------------------------
+def run_count(args, peaks, peaks_kind) -> None:
+    import fma_b200
+    from fma_b200 import _native
+
+    dev = torch.device("cuda:0")
+    n, E = 1 << 24, 128
+    sys.path.insert(0, str(ROOT / "tests"))
+    from _util import zipf_ids
+
+    results = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+    for dist_name, ids in (("uniform", torch.randint(0, E, (n,), dtype=torch.int32, generator=torch.Generator().manual_seed(0))),
+                           ("zipf1.1", zipf_ids(n, E, 1.1, seed=1))):
+        ids_d = ids.to(dev)
+        ref = torch.bincount(ids.long(), minlength=E)
+        for variant in (0, 1):
+            out = fma_b200.continuous_count(ids_d, E, _variant=variant)
+            assert torch.equal(out.to(torch.int64).cpu(), ref)
+            times = []
+            for i in range(args.warmup + args.steps):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fma_b200.continuous_count(ids_d, E, _variant=variant)
+                b.record()
+                torch.cuda.synchronize()
+                if i >= args.warmup:
+                    times.append(a.elapsed_time(b))
+            ms = float(np.median(times))
+            gbs = (n * 4 + E * 4) / ms / 1e6
+            results[f"{dist_name}/variant{variant}"] = {"ms": ms, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]}
+    t0 = time.perf_counter()
+    for _ in range(5):
+        torch.bincount(ids.long(), minlength=E)
+    cpu_ms = (time.perf_counter() - t0) / 5 * 1e3
+    best = results["uniform/variant0"]
+    line = {
+        "metric": "continuous_count_GBps", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+        "config": {"workload": "count_c2", "n": n, "bins": E, "l2": "flushed between iterations (256 MB write)"},
+        "roofline": {"bound": "hbm", "achieved": best["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": best["gbs"] / peaks["hbm_gbs"], "traffic": None, "peak_kind": peaks_kind},
+        "variants": results,
+        "cpu_baseline": {"value": (n * 4 + E * 4) / cpu_ms / 1e6, "unit": "GB/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": "torch.bincount of the full 2^24 ids (includes the int64 cast)"},
+        "gpu_launches": _native.launch_count,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# main arm
+# ---------------------------------------------------------------------------------------------
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="ep_c5", choices=list(WORKLOADS) + ["count_c2"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="override T (for quick runs and profiler captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.tokens else args.warmup
+    peaks, peaks_kind = load_peaks()
+
+    if args.workload == "count_c2":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "count_c2 reports its CPU baseline inline"}))
+            return
+        run_count(args, peaks, peaks_kind)
+        return
+
+    cfg = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        cfg["T"] = args.tokens
+    if args.impl == "reference":
+        run_reference(args, cfg, args.workload)
+        return
+
+    import fma_b200  # noqa: F401
+    from fma_b200 import _native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if world > 1 and args.workload != "ep_c5":
+        raise SystemExit("only the ep_c5 workload is expert-parallel")
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    layer, dtype = make_layer(cfg, rank, world, device)
+    x, dy = make_inputs(cfg, rank, device, dtype)
+    x.requires_grad_(True)
+    T = cfg["T"]
+
+    # ---- device-resident timing -------------------------------------------------------------
+    for _ in range(args.warmup):
+        layer_step(layer, x, dy)
+    barrier()
+    launches_before = _native.launch_count
+    _native.enable_timing(True)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        layer_step(layer, x, dy)
+    end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = start.elapsed_time(end)
+    kernel_times = _native.collect_timing()
+    _native.enable_timing(False)
+    launches = _native.launch_count - launches_before
+    status = _native.device_status()
+    if status != 0:
+        raise SystemExit(f"a kernel reported device status {status:#x}")
+    if world > 1:
+        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * T / (ms_step / 1e3)
+
+    # ---- end to end with host buffers -------------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        x_host = x.detach().cpu().pin_memory()
+        dy_host = dy.detach().cpu().pin_memory()
+        y_host = torch.empty_like(x_host).pin_memory()
+        dx_host = torch.empty_like(x_host).pin_memory()
+        copy_stream = torch.cuda.Stream(device)
+        main_stream = torch.cuda.current_stream(device)
+
+        def e2e_step():
+            for p in layer.parameters():
+                p.grad = None
+            xd = x_host.to(device, non_blocking=True).requires_grad_(True)
+            with torch.cuda.stream(copy_stream):  # dy rides along while the forward runs
+                dyd = dy_host.to(device, non_blocking=True)
+                dy_ready = torch.cuda.Event()
+                dy_ready.record(copy_stream)
+            y, _ = layer(xd)
+            y_ready = torch.cuda.Event()
+            y_ready.record(main_stream)
+            with torch.cuda.stream(copy_stream):  # y goes back to the host while the backward runs
+                copy_stream.wait_event(y_ready)
+                y_host.copy_(y.detach(), non_blocking=True)
+                y.record_stream(copy_stream)
+            main_stream.wait_event(dy_ready)
+            dyd.record_stream(main_stream)
+            y.backward(dyd)
+            dx_host.copy_(xd.grad, non_blocking=True)
+            main_stream.wait_stream(copy_stream)  # the step ends when every copy has landed
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        t1.record()
+        barrier()
+        e2e_ms = t0.elapsed_time(t1)
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        nbytes = x_host.numel() * x_host.element_size()
+        e2e = {"value": world * T / (e2e_ms / args.steps / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
+               "d2h_bytes_per_step": 2 * nbytes, "ms_per_step": e2e_ms / args.steps}  # fmt: skip
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline accounting ----------------------------------------------------------------
+    work = algorithmic_work(cfg)
+    tensor_peak = peaks["bf16_tflops_sustained"] if cfg["dtype"] == "bf16" else None
+    kernels = {}
+    gemm_ms = 0.0
+    gemm_flops = 0
+    for name, (calls, ms) in sorted(kernel_times.items()):
+        per_step = ms / args.steps
+        entry = {"calls_per_step": calls / args.steps, "ms_per_step": per_step}
+        if name in work["gemm_flops"]:
+            # per-rank FLOPs: every rank processes T*k rows in expectation under a uniform router
+            fl = work["gemm_flops"][name]
+            entry.update(achieved=fl / per_step / 1e9, unit="TFLOP/s")
+            if tensor_peak:
+                entry["frac"] = entry["achieved"] / tensor_peak
+            gemm_ms += per_step
+            gemm_flops += fl
+        elif name in work["hbm_bytes"]:
+            by = work["hbm_bytes"][name]
+            entry.update(achieved=by / per_step / 1e6, unit="GB/s", frac=by / per_step / 1e6 / peaks["hbm_gbs"])
+        kernels[name] = entry
+    roofline = None
+    if gemm_ms > 0:
+        achieved = gemm_flops / gemm_ms / 1e9
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": (achieved / tensor_peak) if tensor_peak else None, "traffic": None,
+                    "kernel": "gemm_tc_kernel (6 launches per step)" if cfg["dtype"] == "bf16" else "gemm_simt_kernel",
+                    "peak_kind": f"{peaks_kind} sustained cuBLAS bf16", "gemm_ms_per_step": gemm_ms,
+                    "gemm_share_of_step": gemm_ms / ms_step}  # fmt: skip
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        weights = host_weights_from_layer(layer)
+        cpu_oracle_pass({**cfg, "T": min(cfg["T"], 64)}, weights, seed=0)  # warm the BLAS threads
+        secs, toks = cpu_oracle_pass(cfg, weights, seed=1)
+        cpu_baseline = {"value": toks / secs, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+                        "sample": f"one forward+backward of {toks} tokens over all {cfg['E']} experts "
+                                  f"({secs:.1f} s), numpy with {cfg['dtype']} rounding points"}  # fmt: skip
+
+    line = {
+        "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+        "config": {"workload": args.workload, **{k: cfg[k] for k in ("T", "H", "E", "k", "I")},
+                   "tokens_per_gpu": T, "router": cfg["router"],
+                   "parallelism": f"ep{world}" if world > 1 else "single",
+                   "l2": "inputs larger than L2 (x alone is %d MB)" % (x.numel() * x.element_size() >> 20)},
+        "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": launches,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

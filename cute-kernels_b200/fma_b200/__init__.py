@@ -7,7 +7,7 @@ C ABI (see include/fma_b200.h); there is no Triton, eager-PyTorch or CPU fallbac
 
 from . import _native
 from .kernel_backend import KernelBackend
-from .modules import Experts, MoE
+from .modules import Experts, ExpertParallelMoE, MoE, shard_expert_state_dict, unshard_expert_state_dicts
 from .ops import continuous_count, grouped_gemm, swiglu, swiglu_packed
 from .utils import ceil_divide, ensure_contiguous, set_seed
 
@@ -15,6 +15,9 @@ __all__ = [
     "KernelBackend",
     "MoE",
     "Experts",
+    "ExpertParallelMoE",
+    "shard_expert_state_dict",
+    "unshard_expert_state_dicts",
     "continuous_count",
     "grouped_gemm",
     "swiglu",

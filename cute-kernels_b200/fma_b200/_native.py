@@ -82,10 +82,45 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+# Kernels launched per entry-point call (the sort is three kernels; status queries launch none).
+KERNELS_PER_CALL = {"fma_b200_moe_sort": 3, "fma_b200_device_status": 0}
+launch_count = 0  # kernels launched through this binding since import (a plain counter for benchmarks)
+_timing: dict[str, list] | None = None  # entry point -> [(start event, end event)], when enabled
+
+
+def enable_timing(enabled: bool) -> None:
+    """Benchmark hook: bracket every entry-point call with CUDA events on the launching stream."""
+    global _timing
+    _timing = {} if enabled else None
+
+
+def collect_timing() -> dict[str, tuple[int, float]]:
+    """Returns {entry point: (calls, total milliseconds)} and clears the record.  Synchronises."""
+    global _timing
+    out: dict[str, tuple[int, float]] = {}
+    if _timing is None:
+        return out
+    torch.cuda.synchronize()
+    for name, pairs in _timing.items():
+        out[name] = (len(pairs), sum(a.elapsed_time(b) for a, b in pairs))
+    _timing = {}
+    return out
+
+
 def call(name: str, *args) -> None:
     """Calls an int-status entry point and raises RuntimeError on a non-zero status."""
+    global launch_count
     handle = lib()
-    status = getattr(handle, name)(*args)
+    launch_count += KERNELS_PER_CALL.get(name, 1)
+    if _timing is not None and KERNELS_PER_CALL.get(name, 1) > 0:
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        status = getattr(handle, name)(*args)
+        end.record()
+        _timing.setdefault(name, []).append((start, end))
+    else:
+        status = getattr(handle, name)(*args)
     if status != 0:
         text = handle.fma_b200_status_string(status).decode()
         detail = handle.fma_b200_last_error().decode()

@@ -130,6 +130,8 @@ def gemm_dgrad(dY: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor) ->
 def gemm_wgrad(dY: torch.Tensor, X: torch.Tensor, E: int, seg_offsets: torch.Tensor, n_seg: int = 1) -> torch.Tensor:
     rows, OUT = dY.shape
     IN = X.size(1)
+    if rows == 0:  # no rows at all (an expert-parallel rank that received nothing)
+        return torch.zeros(E, OUT, IN, dtype=dY.dtype, device=dY.device)
     dW = torch.empty(E, OUT, IN, dtype=dY.dtype, device=dY.device)
     call("fma_b200_moe_gemm_wgrad", ptr(dY), ptr(X), ptr(dW), dtype_code(dY.dtype), rows, E, OUT, IN,
          ptr(seg_offsets), n_seg, stream_ptr(dY.device))  # fmt: skip
