@@ -151,6 +151,58 @@ static int launch_count(const void* ids, int64_t n, int size, uint32_t* out, voi
     return check_launch("continuous_count");
 }
 
+// ---------------------------------------------------------------------------
+// Variant for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------
+// Some callers of this library have no way to obtain scratch memory at the point of the call:
+// a plugin loaded into a host whose device heap is owned by someone else (an inference server's
+// arena, another framework's caching allocator), code running inside a region where cudaMalloc
+// would synchronise the device and break the host's stream ordering, or a small C program that
+// links the library and wants a histogram without writing an allocator.  For them the ticket and
+// the block partials live in this file-scope array instead of a caller-provided workspace.  Every
+// GPU that loads the library holds these 2 MiB + 256 B until the process exits.
+constexpr int kStaticCountMaxBins = 1024;                 // largest `size` the static variant accepts
+constexpr int kStaticCountPartialWords = 512 * 1024;      // grid * size never exceeds this
+static __device__ __align__(256) uint32_t g_static_count_scratch[64 + kStaticCountPartialWords];
+
+// In host code `g_static_count_scratch` is only a handle for the runtime, not a device address, so
+// the address the kernel needs is looked up once per device (with that device current) and cached.
+static int static_count_scratch(uint32_t** out) {
+    static uint32_t* cached[64] = {nullptr};
+    int dev = -1;
+    FMAB_CUDA(cudaGetDevice(&dev));
+    FMAB_REQUIRE(dev >= 0 && dev < 64, FMA_B200_ERR_BAD_ARG, "device ordinal %d is outside [0,64)", dev);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_count_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(FMA_B200_ERR_LAUNCH, "cudaGetSymbolAddress(static count scratch): %s", cudaGetErrorString(e));
+        cached[dev] = static_cast<uint32_t*>(p);
+    }
+    *out = cached[dev];
+    return FMA_B200_OK;
+}
+
+template <typename IdT>
+static int launch_count_static(const void* ids, int64_t n, int size, uint32_t* out, uint32_t* scratch,
+                               cudaStream_t stream) {
+    constexpr int kPerVec = 16 / sizeof(IdT);
+    const int pitch = ((size + 31) / 32) * 32 + 1;
+    int copies = 32;
+    while (copies > 1 && static_cast<int64_t>(copies) * pitch * 4 > 48 * 1024) copies >>= 1;
+    const int64_t smem = static_cast<int64_t>(copies) * pitch * 4;  // <= 48 KB for size <= 1024: no opt-in needed
+    const int64_t n_vec = n / kPerVec;
+    int64_t want = (n_vec + 4LL * kCountThreads - 1) / (4LL * kCountThreads);
+    int64_t cap = static_cast<int64_t>(sm_count()) * ((smem > 24 * 1024) ? 2 : 4);
+    if (cap > kStaticCountPartialWords / size) cap = kStaticCountPartialWords / size;  // partials must fit the array
+    const int grid = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+    // word 0 is the ticket (zero at load, reset to zero by the last block of every call);
+    // the partials start 256 bytes in and are fully rewritten by each call before they are read
+    continuous_count_kernel<IdT, false><<<grid, kCountThreads, smem, stream>>>(
+        static_cast<const IdT*>(ids), n, size, copies, pitch, out, scratch, scratch + 64);
+    return check_launch("continuous_count_static");
+}
+
 }  // namespace fmab
 
 extern "C" {
@@ -181,6 +233,25 @@ int fma_b200_continuous_count_variant(const void* ids, int32_t id_bytes, int64_t
 int fma_b200_continuous_count(const void* ids, int32_t id_bytes, int64_t n, int32_t size, uint32_t* out,
                               void* workspace, int64_t workspace_bytes, void* stream) {
     return fma_b200_continuous_count_variant(ids, id_bytes, n, size, out, workspace, workspace_bytes, 0, stream);
+}
+
+int fma_b200_continuous_count_static(const void* ids, int32_t id_bytes, int64_t n, int32_t size, uint32_t* out,
+                                     void* stream) {
+    using namespace fmab;
+    FMAB_REQUIRE(out != nullptr, FMA_B200_ERR_BAD_ARG, "out is NULL");
+    FMAB_REQUIRE(n >= 0 && n < (1LL << 40), FMA_B200_ERR_BAD_ARG, "n=%lld out of range", (long long)n);
+    FMAB_REQUIRE(n == 0 || ids != nullptr, FMA_B200_ERR_BAD_ARG, "ids is NULL");
+    FMAB_REQUIRE(size >= 1, FMA_B200_ERR_BAD_ARG, "size=%d must be positive", size);
+    FMAB_REQUIRE(size <= kStaticCountMaxBins, FMA_B200_ERR_BAD_ARG,
+                 "size=%d exceeds the %d bins the built-in scratch array supports; use fma_b200_continuous_count "
+                 "with a caller-provided workspace", size, kStaticCountMaxBins);
+    FMAB_REQUIRE(id_bytes == 4 || id_bytes == 8, FMA_B200_ERR_UNSUPPORTED, "ids must be int32 or int64");
+    FMAB_REQUIRE(aligned16(ids), FMA_B200_ERR_BAD_ARG, "ids not 16-byte aligned");
+    uint32_t* scratch = nullptr;
+    if (int rc = static_count_scratch(&scratch)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (id_bytes == 4) return launch_count_static<int32_t>(ids, n, size, out, scratch, s);
+    return launch_count_static<int64_t>(ids, n, size, out, scratch, s);
 }
 
 }  // extern "C"

@@ -30,6 +30,7 @@ SIGNATURES: dict[str, tuple] = {
     "fma_b200_continuous_count_workspace_bytes": (_I64, [_I32]),
     "fma_b200_continuous_count": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P, _I64, _P]),
     "fma_b200_continuous_count_variant": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P, _I64, _I32, _P]),
+    "fma_b200_continuous_count_static": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P]),
     "fma_b200_router_topk_softmax": (ctypes.c_int, [_P, _I32, _I64, _I32, _I32, _P, _P, _P]),
     "fma_b200_router_topk_softmax_backward": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _P, _P]),
     "fma_b200_moe_rows_cap": (_I64, [_I64, _I32, _I32]),

@@ -77,6 +77,27 @@ int fma_b200_continuous_count(const void* ids, int32_t id_bytes, int64_t n, int3
 int fma_b200_continuous_count_variant(const void* ids, int32_t id_bytes, int64_t n, int32_t size, uint32_t* out,
                                       void* workspace, int64_t workspace_bytes, int32_t variant, void* stream);
 
+/*
+ * continuous_count for callers that cannot allocate device memory (no counterpart in the
+ * reference, which allocates its outputs and scratch through torch).  Think of a plugin running
+ * inside a host process whose GPU memory pool belongs to that host, of code on a path where
+ * cudaMalloc's implicit device synchronisation is not acceptable, or of a plain C program that
+ * links this library without an allocator of its own.  The ticket and per-block partials live in a
+ * 2 MiB + 256 B array that is part of the library image (every GPU that loads the library holds
+ * it until the process exits); the caller passes only ids and out.
+ *   - size <= 1024; larger sizes are refused with FMA_B200_ERR_BAD_ARG (use the workspace form).
+ *   - Calls no cudaMalloc / cudaFree or any allocating routine.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU
+ *     (different streams, no ordering between them) race.  Calls ordered on one stream are fine:
+ *     each call rewrites the partials before reading them and leaves the ticket at zero.
+ * Results are identical to fma_b200_continuous_count.
+ */
+int fma_b200_continuous_count_static(const void* ids, int32_t id_bytes, int64_t n, int32_t size, uint32_t* out,
+                                     void* stream);
+
 /* ======================================================================= */
 /* router: top-k + softmax over the selected logits                         */
 /* ======================================================================= */
