@@ -14,7 +14,7 @@
 // Operands may be K-major (the reduction index is contiguous in memory) or MN-major (the row /
 // column index is contiguous); the latter is what dgrad (B = W[e], [K,N] row-major) and wgrad
 // (A = dY^T, B = X, both [tokens, features] row-major) need, so no transposed copies are made.
-// No TMA multicast and no thread-block clusters are used anywhere in this file.
+// Every TMA load targets the issuing CTA's own shared memory; no thread-block clusters are used.
 //
 // Every mbarrier wait is bounded (about one second of %globaltimer); a wait that runs out sets
 // the device status word, raises a CTA-wide abort flag that all other waits poll, and the CTA

@@ -1,0 +1,103 @@
+"""Expert-parallel plumbing on CPU: two gloo ranks run the product's count exchange, split-size
+computation and row all-to-all (fma_b200.modules.moe_ep) on padded grouped layouts, with the numpy
+oracle standing in for the CUDA kernels, and must reproduce the single-process oracle output for
+their own tokens."""
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, result_dir: str):
+    for p in (ROOT / "cute-kernels_b200", ROOT):
+        sys.path.insert(0, str(p))
+    from fma_b200.modules import moe_ep
+    from oracle import moe_oracle as O
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        T, H, E, k, I = 150 + 37 * rank, 32, 8, 3, 16
+        El = E // world
+        rng = np.random.default_rng(5)  # weights: common to all ranks
+        w_gate = rng.standard_normal((E, H), dtype=np.float32) * 0.5
+        w_fc = rng.standard_normal((E, 2 * I, H), dtype=np.float32) * 0.1
+        w_proj = rng.standard_normal((E, H, I), dtype=np.float32) * 0.1
+        x = np.random.default_rng(100 + rank).standard_normal((T, H), dtype=np.float32)
+        ref = O.moe_forward(x, w_gate, w_fc, w_proj, k, "f32")  # all experts, this rank's tokens
+
+        maps = O.row_maps(ref["selected"], E, 128)
+        total = int(maps["pad_offsets"][-1])
+        xg = np.zeros((maps["rows_cap"], H), np.float32)
+        xg[maps["row_of_slot"]] = np.repeat(x, k, axis=0)
+
+        counts = torch.from_numpy(maps["expert_count"].astype(np.int64))
+        recv_counts = moe_ep.exchange_counts(counts, world, None)
+        assert recv_counts.shape == (world, El) and recv_counts.dtype == torch.int32
+        # what every source really holds for my experts
+        gathered = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(gathered, counts)
+        for s in range(world):
+            assert recv_counts[s].tolist() == gathered[s][rank * El : (rank + 1) * El].tolist()
+        send_rows, recv_rows = moe_ep.split_sizes(counts, recv_counts, world)
+        assert sum(send_rows) == total and all(r % 128 == 0 for r in send_rows + recv_rows)
+
+        recv = moe_ep.all_to_all_rows(torch.from_numpy(xg), send_rows, recv_rows, None).numpy()
+        # receive-side maps (what fma_b200_moe_ep_recv_maps computes on the GPU)
+        seg = np.concatenate([[0], np.cumsum(-(-recv_counts.numpy().reshape(-1) // 128) * 128)])
+        out = np.zeros((recv.shape[0], H), np.float32)
+        for s in range(world):
+            for e in range(El):
+                a, n = seg[s * El + e], int(recv_counts[s, e])
+                rows = recv[a : a + n]
+                assert np.all(recv[a + n : seg[s * El + e + 1]] == 0)  # padding arrives as zeros
+                ge = rank * El + e
+                pre = rows @ w_fc[ge].T
+                out[a : a + n] = O.swiglu_packed(pre, "f32") @ w_proj[ge].T
+        back = moe_ep.all_to_all_rows(torch.from_numpy(out), recv_rows, send_rows, None).numpy()
+        rows_of = maps["row_of_slot"].reshape(T, k)
+        y = (back[rows_of] * ref["weights"][:, :, None]).sum(1)
+        err = O.rel_l2(y, ref["y"])
+        assert err < 1e-5, err
+        Path(result_dir, f"ok{rank}").write_text(f"{err}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_exchange_two_gloo_ranks(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_shard_and_unshard_state_dict_round_trip():
+    sys.path.insert(0, str(ROOT / "cute-kernels_b200"))
+    import fma_b200
+
+    full = fma_b200.MoE(8, 2, 32, 16, fma_b200.swiglu_packed, True, False, 0.02).state_dict()
+    shards = [fma_b200.shard_expert_state_dict(full, r, 4) for r in range(4)]
+    assert shards[1]["c_fc.weight"].shape == (2, 32, 32) and shards[1]["gate.weight"].shape == (8, 32)
+    assert torch.equal(shards[2]["c_proj.weight"], full["c_proj.weight"][4:6])
+    back = fma_b200.unshard_expert_state_dicts(shards)
+    assert list(back) == list(full)
+    for key in full:
+        assert torch.equal(back[key], full[key]), key
+    # a shard loads strictly into an expert-parallel layer of the same local size (group size 1 here)
+    local = fma_b200.MoE(2, 2, 32, 16, fma_b200.swiglu_packed, True, False, 0.02)
+    sd = dict(shards[0])
+    sd["gate.weight"] = sd["gate.weight"][:2]
+    local.load_state_dict(sd, strict=True)

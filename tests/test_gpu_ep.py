@@ -1,0 +1,86 @@
+"""Expert-parallel MoE on 2 GPUs (NCCL all-to-all) against the single-GPU layer holding all experts.
+Skipped on a box with one GPU."""
+
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rel(a, b):
+    return float((a.double() - b.double()).norm() / b.double().norm())
+
+
+def _worker(rank: int, world: int, port: int, result_dir: str):
+    import torch.distributed as dist
+
+    for p in (ROOT / "cute-kernels_b200", ROOT / "tests"):
+        sys.path.insert(0, str(p))
+    import fma_b200
+    from _util import randn
+
+    dev = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    try:
+        dtype = torch.bfloat16
+        T, H, E, k, I = 700, 256, 16, 4, 128
+        full = fma_b200.MoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02)
+        with torch.no_grad():
+            full.gate.weight.copy_(randn((E, H), torch.float32, 1, 0.02))
+            full.c_fc.weight.copy_(randn((E, 2 * I, H), torch.float32, 2, 0.02))
+            full.c_proj.weight.copy_(randn((E, H, I), torch.float32, 3, 0.02))
+        full = full.to(dev).to(dtype)
+        ep = fma_b200.ExpertParallelMoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02)
+        shard = fma_b200.shard_expert_state_dict(full.state_dict(), rank, world)
+        ep = ep.to(dev).to(dtype)
+        ep.load_state_dict(shard, strict=True)
+
+        xs = [randn((T + 64 * r, H), dtype, 10 + r).to(dev) for r in range(world)]  # ragged T per rank
+        gs = [randn((T + 64 * r, H), dtype, 20 + r).to(dev) for r in range(world)]
+        x = xs[rank].clone().requires_grad_(True)
+        y, logits = ep(x)
+        y.backward(gs[rank])
+        torch.cuda.synchronize()
+
+        x_all = torch.cat(xs).requires_grad_(True)
+        y_all, logits_all = full(x_all)
+        y_all.backward(torch.cat(gs))
+        lo = sum(t.size(0) for t in xs[:rank])
+        hi = lo + xs[rank].size(0)
+        assert torch.equal(logits, logits_all[lo:hi])
+        e0, e1 = ep.local_expert_range()
+        errs = {
+            "y": _rel(y, y_all[lo:hi]),
+            "dx": _rel(x.grad, x_all.grad[lo:hi]),
+            "d_w_fc": _rel(ep.c_fc.weight.grad, full.c_fc.weight.grad[e0:e1]),
+            "d_w_proj": _rel(ep.c_proj.weight.grad, full.c_proj.weight.grad[e0:e1]),
+        }
+        assert all(v <= 1e-2 for v in errs.values()), errs
+        # y is a per-token computation: the expert-parallel result matches the local one bit for bit
+        assert torch.equal(y, y_all[lo:hi])
+        from fma_b200 import _native
+
+        assert _native.device_status() == 0
+        Path(result_dir, f"ok{rank}").write_text(str(errs))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_matches_single_gpu(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
