@@ -1,13 +1,14 @@
 // bf16 grouped GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
 //
-// One persistent CTA per SM, 192 threads, warp-specialised:
+// One persistent CTA per SM, 320 threads, warp-specialised:
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of A/B k-blocks into a 4-stage
 //               shared-memory ring (128-byte swizzle), signalled by mbarrier transaction counts;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, bf16 in, fp32
 //               accumulate in tensor memory); tcgen05.commit releases ring stages and publishes
 //               finished accumulators;
-//   warps 2-5   epilogue: tcgen05.ld of the accumulator (one TMEM lane = one output row per
-//               thread), optional SwiGLU forward / backward math, bf16 rounding, 128-bit stores.
+//   warps 2-9   epilogue: tcgen05.ld of the accumulator (one TMEM lane = one output row per
+//               thread; warps 2-5 take the first half of the tile's columns, warps 6-9 the second),
+//               optional SwiGLU forward / backward math, bf16 rounding, 128-bit stores.
 // Tensor memory holds two 128x256 fp32 accumulators (all 512 columns), so the epilogue of tile
 // i overlaps the main loop of tile i+1.
 //
@@ -20,6 +21,7 @@
 // the device status word, raises a CTA-wide abort flag that all other waits poll, and the CTA
 // leaves through the normal teardown (tensor memory is released).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <vector>
 
@@ -38,7 +40,7 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int MAX_GEMM_THREADS = 320;  // 2 + 8 warps; the 4-epilogue-warp build uses 192
 constexpr int TMEM_COLS = 512;
 constexpr int SUPER_M = 16;       // m-tiles walked together so that concurrent CTAs share operand tiles in L2
 constexpr size_t GEMM_SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;
@@ -222,16 +224,27 @@ struct Tile {
     int64_t ldd;
 };
 
-template <bool B_MN, int EPI>
-__device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, Tile& t) {
-    // Walk SUPER_M m-tiles together, n-tile by n-tile.
+// m-tile index of a linear tile id (SUPER_M m-tiles are walked together, n-tile by n-tile).
+__device__ __forceinline__ int tile_to_mtile(const GemmParams& p, int tile, int& nt) {
     const int per_super = SUPER_M * p.n_ntiles;
     const int super = tile / per_super;
     const int m_first = super * SUPER_M;
     const int m_span = min(SUPER_M, p.n_mtiles - m_first);
     const int r = tile - super * per_super;
-    const int nt = r / m_span;
-    const int mt = m_first + (r - nt * m_span);
+    nt = r / m_span;
+    return m_first + (r - nt * m_span);
+}
+// Rows mode: the expert id of a tile, loaded early so that its latency hides behind the previous tile.
+__device__ __forceinline__ int peek_expert(const GemmParams& p, int tile, int total_tiles) {
+    if (p.mode != MODE_ROWS || tile >= total_tiles) return -1;
+    int nt;
+    return __ldg(p.mtile_expert + tile_to_mtile(p, tile, nt));
+}
+
+template <bool B_MN, int EPI>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int expert_hint, Tile& t) {
+    int nt;
+    const int mt = tile_to_mtile(p, tile, nt);
     constexpr int n_step = (EPI == EPI_SWIGLU_FWD) ? BN / 2 : BN;
     t.n0 = nt * n_step;
     t.map_a = &p.map_a;
@@ -240,7 +253,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, Tile&
     t.d_base = 0;
     t.ldd = p.ldd;
     if (p.mode == MODE_ROWS) {
-        const int e = p.mtile_expert[mt];
+        const int e = expert_hint;  // == mtile_expert[mt], fetched one tile ahead
         if (e < 0) return false;
         t.group = e;
         t.a_mn = mt * BM;
@@ -322,8 +335,8 @@ __device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float*
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmParams p) {
+template <bool A_MN, bool B_MN, int EPI, int EPI_WARPS>
+__global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -344,7 +357,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&acc_full_bar[b]), 1);
-            mbar_init(smem_u32(&acc_empty_bar[b]), 4);  // one arrival per epilogue warp
+            mbar_init(smem_u32(&acc_empty_bar[b]), EPI_WARPS);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -370,9 +383,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
+            int e_next = peek_expert(p, blockIdx.x, total_tiles);
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
                 Tile t;
-                if (!decode_tile<B_MN, EPI>(p, tile, t)) continue;
+                const int e_cur = e_next;
+                e_next = peek_expert(p, tile + gridDim.x, total_tiles);
+                if (!decode_tile<B_MN, EPI>(p, tile, e_cur, t)) continue;
                 if (p.mode == MODE_GENERAL) {
                     tensormap_acquire(t.map_a);
                     tensormap_acquire(t.map_b);
@@ -428,9 +444,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
             int buf = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
+            int e_next = peek_expert(p, blockIdx.x, total_tiles);
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
                 Tile t;
-                if (!decode_tile<B_MN, EPI>(p, tile, t)) continue;
+                const int e_cur = e_next;
+                e_next = peek_expert(p, tile + gridDim.x, total_tiles);
+                if (!decode_tile<B_MN, EPI>(p, tile, e_cur, t)) continue;
                 if (!mbar_wait(smem_u32(&acc_empty_bar[buf]), acc_phase ^ 1u, abort_ptr, p.status)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
@@ -472,13 +491,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are visible to this warp
+        const int quad = warp & 3;          // TMEM lanes [32*quad, 32*quad+32) are visible to this warp
+        constexpr int kColSplit = EPI_WARPS / 4;  // 1: every warp stores all columns of its rows; 2: half each
+        const int half = (warp - 2) >> 2;         // which part of the tile's columns this warp stores
         const int row_in_tile = quad * 32 + lane;
         int buf = 0;
         uint32_t acc_phase = 0;
+        int e_next = peek_expert(p, blockIdx.x, total_tiles);
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             Tile t;
-            if (!decode_tile<B_MN, EPI>(p, tile, t)) continue;
+            const int e_cur = e_next;
+            e_next = peek_expert(p, tile + gridDim.x, total_tiles);
+            if (!decode_tile<B_MN, EPI>(p, tile, e_cur, t)) continue;
             // Does this tile have any reduction work?  (Same test as the MMA issuer's.)
             bool any_k = false;
             for (int s = 0; s < n_seg; ++s) {
@@ -494,8 +518,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 
             if (EPI == EPI_PLAIN) {
                 __nv_bfloat16* drow = p.d + t.d_base + grow * t.ldd + t.n0;
+                constexpr int kChunks = BN / 32 / kColSplit;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = half * kChunks; c < (half + 1) * kChunks; ++c) {
                     const int cols_left = t.n_valid - c * 32;
                     if (cols_left <= 0) break;
                     float v[32];
@@ -511,8 +536,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                 // accumulator columns [0,128) = up, [128,256) = gate, for act columns n0..n0+127
                 __nv_bfloat16* arow = p.d + grow * p.ldd + t.n0;
                 __nv_bfloat16* prow = p.d2 ? p.d2 + grow * (2 * static_cast<int64_t>(p.inter)) + t.n0 : nullptr;
+                constexpr int kChunks = BN / 64 / kColSplit;
 #pragma unroll 1
-                for (int c = 0; c < BN / 64; ++c) {
+                for (int c = half * kChunks; c < (half + 1) * kChunks; ++c) {
                     const int cols_left = t.n_valid - c * 32;
                     if (cols_left <= 0) break;
                     float u[32], g[32];
@@ -532,18 +558,36 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                     if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
                 }
             } else {
-                // d_act tile -> d_up, d_gate using the saved pre-activations
+                // d_act tile -> d_up, d_gate using the saved pre-activations.  The up/gate values of the
+                // next 32 columns are fetched while the current ones are processed.
                 const __nv_bfloat16* prow = p.pre + grow * (2 * static_cast<int64_t>(p.inter)) + t.n0;
                 __nv_bfloat16* drow = p.d + grow * (2 * static_cast<int64_t>(p.inter)) + t.n0;
+                constexpr int kChunks = BN / 32 / kColSplit;
+                const int c_begin = half * kChunks, c_end = (half + 1) * kChunks;
+                uint4 nu[4], ng[4];
+                auto fetch = [&](int c) {
+                    const int cols_left = t.n_valid - c * 32;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const bool ok = row_ok && q * 8 < cols_left;
+                        nu[q] = ok ? ld_global_16(prow + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
+                        ng[q] = ok ? ld_global_16(prow + p.inter + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
+                    }
+                };
+                fetch(c_begin);
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = c_begin; c < c_end; ++c) {
                     const int cols_left = t.n_valid - c * 32;
                     if (cols_left <= 0) break;
                     float da[32], u[32], g[32];
                     tc_load_32(taddr + c * 32, da);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        Elem<__nv_bfloat16>::unpack(nu[q], u + q * 8);
+                        Elem<__nv_bfloat16>::unpack(ng[q], g + q * 8);
+                    }
+                    if (c + 1 < c_end) fetch(c + 1);
                     if (row_ok) {
-                        load_row32_bf16(prow + c * 32, u, cols_left);
-                        load_row32_bf16(prow + p.inter + c * 32, g, cols_left);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const float d = round_bf16(da[i]);
@@ -616,10 +660,21 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
     return FMA_B200_OK;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
-static int launch_gemm(const GemmParams& p, cudaStream_t s) {
+// Epilogue width: 8 warps (two per TMEM lane quadrant) by default; FMA_B200_GEMM_EPI_WARPS=4 selects
+// the narrower build (a tuning knob for measurements).
+static int epilogue_warps() {
+    static int cached = 0;
+    if (cached == 0) {
+        const char* env = getenv("FMA_B200_GEMM_EPI_WARPS");
+        cached = (env != nullptr && atoi(env) == 4) ? 4 : 8;
+    }
+    return cached;
+}
+
+template <bool A_MN, bool B_MN, int EPI, int EPI_WARPS>
+static int launch_gemm_w(const GemmParams& p, cudaStream_t s) {
     static bool configured = false;
-    auto kernel = gemm_tc_kernel<A_MN, B_MN, EPI>;
+    auto kernel = gemm_tc_kernel<A_MN, B_MN, EPI, EPI_WARPS>;
     if (!configured) {
         FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
         configured = true;
@@ -628,8 +683,14 @@ static int launch_gemm(const GemmParams& p, cudaStream_t s) {
     if (total <= 0) return FMA_B200_OK;
     FMAB_REQUIRE(total < (1LL << 31), FMA_B200_ERR_BAD_ARG, "too many tiles");
     const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
-    kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(p);
+    kernel<<<grid, 64 + 32 * EPI_WARPS, GEMM_SMEM_BYTES, s>>>(p);
     return check_launch("grouped GEMM (tcgen05)");
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const GemmParams& p, cudaStream_t s) {
+    if (epilogue_warps() == 4) return launch_gemm_w<A_MN, B_MN, EPI, 4>(p, s);
+    return launch_gemm_w<A_MN, B_MN, EPI, 8>(p, s);
 }
 
 static int fill_common(GemmParams& p) {

@@ -138,17 +138,32 @@ combine_backward_kernel(const T* __restrict__ dy, const T* __restrict__ expert_o
         uint4* dst = reinterpret_cast<uint4*>(d_expert_out + row * H);
         const uint4* o_src = want_dw ? reinterpret_cast<const uint4*>(expert_out + row * H) : nullptr;
         float dot = 0.f;
-        for (int c = lane; c < n_vec; c += 32) {
-            float g[V], o[V], r[V];
-            // dy's row is re-read for every j; after the first pass it sits in L1/L2.
-            Elem<T>::unpack(ld_global_16(g_src + c), g);
+        for (int c0 = 0; c0 < n_vec; c0 += 128) {
+            // four independent 16-byte loads of dy (L1/L2 after the first j) and of expert_out in flight
+            uint4 gv[4], ov[4];
 #pragma unroll
-            for (int i = 0; i < V; ++i) r[i] = w * g[i];
-            dst[c] = Elem<T>::pack(r);
-            if (want_dw) {
-                Elem<T>::unpack(ld_stream_16(o_src + c), o);
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * 32 + lane;
+                if (c < n_vec) {
+                    gv[u] = ld_global_16(g_src + c);
+                    if (want_dw) ov[u] = ld_stream_16(o_src + c);
+                }
+            }
 #pragma unroll
-                for (int i = 0; i < V; ++i) dot = fmaf(o[i], g[i], dot);
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * 32 + lane;
+                if (c < n_vec) {
+                    float g[V], o[V], r[V];
+                    Elem<T>::unpack(gv[u], g);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) r[i] = w * g[i];
+                    dst[c] = Elem<T>::pack(r);
+                    if (want_dw) {
+                        Elem<T>::unpack(ov[u], o);
+#pragma unroll
+                        for (int i = 0; i < V; ++i) dot = fmaf(o[i], g[i], dot);
+                    }
+                }
             }
         }
         if (want_dw) {

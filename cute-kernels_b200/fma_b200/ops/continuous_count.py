@@ -24,7 +24,7 @@ def _workspace(device: torch.device, size: int) -> torch.Tensor:
 
 @torch.no_grad()
 def continuous_count(
-    x: torch.Tensor, size: int, *, kernel_backend: KernelBackend = KernelBackend.cuda, _variant: int = 0
+    x: torch.Tensor, size: int, *, kernel_backend: KernelBackend = KernelBackend.cuda, _variant: int | None = None
 ) -> torch.Tensor:
     """Counts the occurrences of the values [0, size) in the 1-D int32/int64 tensor `x`.
 
@@ -43,17 +43,10 @@ def continuous_count(
 
     output = torch.empty(size, dtype=torch.uint32, device=x.device)
     ws = _workspace(x.device, size)
+    args = (_native.ptr(x), x.element_size(), x.numel(), size, _native.ptr(output), _native.ptr(ws), ws.numel())
     with torch.cuda.device(x.device):
-        _native.call(
-            "fma_b200_continuous_count_variant",
-            _native.ptr(x),
-            x.element_size(),
-            x.numel(),
-            size,
-            _native.ptr(output),
-            _native.ptr(ws),
-            ws.numel(),
-            _variant,
-            _native.stream_ptr(x.device),
-        )
+        if _variant is None:  # the library picks the shared-memory scheme from `size`
+            _native.call("fma_b200_continuous_count", *args, _native.stream_ptr(x.device))
+        else:  # measurement hook: force one scheme
+            _native.call("fma_b200_continuous_count_variant", *args, _variant, _native.stream_ptr(x.device))
     return output

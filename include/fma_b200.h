@@ -60,10 +60,10 @@ int fma_b200_device_status(int32_t* status_out, void* stream);
  * fma/ops/continuous_count/__init__.py:38-39).
  *   ids        int32 (id_bytes == 4) or int64 (id_bytes == 8), n elements, 16-byte aligned
  *   out        uint32[size], fully overwritten
- *   workspace  fma_b200_continuous_count_workspace_bytes(size) bytes, 16-byte aligned.
- *              Its first 128 bytes must be zero before the first call; every call
- *              leaves them zero again, so one workspace can serve all later calls
- *              that do not overlap on the device.
+ *   workspace  fma_b200_continuous_count_workspace_bytes(size) bytes (128 + 32*size), 16-byte
+ *              aligned: a ticket and eight copies of an accumulator.  It must be zero-filled before the first
+ *              call; every call leaves it zero-filled again, so one workspace can serve all
+ *              later calls that do not overlap on the device.
  * size <= 16384, n < 2^40.
  */
 int64_t fma_b200_continuous_count_workspace_bytes(int32_t size);
@@ -71,8 +71,10 @@ int fma_b200_continuous_count(const void* ids, int32_t id_bytes, int64_t n, int3
                               uint32_t* out, void* workspace, int64_t workspace_bytes, void* stream);
 /*
  * Same, with the shared-memory scheme chosen by the caller (for measurement):
- * variant 0 = one sub-histogram per lane (what fma_b200_continuous_count uses),
- * variant 1 = one histogram per block with warp-aggregated (match.any) atomics.
+ * variant 0 = one sub-histogram per lane updated with shared-memory atomics (the default),
+ * variant 1 = one histogram per block with warp-aggregated (match.any) atomics,
+ * variant 2 = a private column per lane of every warp, plain load/add/store (size <= 1024).
+ * fma_b200_continuous_count uses variant 0, the fastest measured on B200.
  */
 int fma_b200_continuous_count_variant(const void* ids, int32_t id_bytes, int64_t n, int32_t size, uint32_t* out,
                                       void* workspace, int64_t workspace_bytes, int32_t variant, void* stream);
@@ -82,9 +84,9 @@ int fma_b200_continuous_count_variant(const void* ids, int32_t id_bytes, int64_t
  * reference, which allocates its outputs and scratch through torch).  Think of a plugin running
  * inside a host process whose GPU memory pool belongs to that host, of code on a path where
  * cudaMalloc's implicit device synchronisation is not acceptable, or of a plain C program that
- * links this library without an allocator of its own.  The ticket and per-block partials live in a
- * 2 MiB + 256 B array that is part of the library image (every GPU that loads the library holds
- * it until the process exits); the caller passes only ids and out.
+ * links this library without an allocator of its own.  The ticket and the accumulators live in a
+ * 32 KiB + 128 B array that is part of the library image (every GPU that loads the library holds it until
+ * the process exits); the caller passes only ids and out.
  *   - size <= 1024; larger sizes are refused with FMA_B200_ERR_BAD_ARG (use the workspace form).
  *   - Calls no cudaMalloc / cudaFree or any allocating routine.
  *   - The first call on each device looks up the array's device address
@@ -92,7 +94,7 @@ int fma_b200_continuous_count_variant(const void* ids, int32_t id_bytes, int64_t
  *     outside any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU
  *     (different streams, no ordering between them) race.  Calls ordered on one stream are fine:
- *     each call rewrites the partials before reading them and leaves the ticket at zero.
+ *     the array is zero when the library is loaded and each call's last block clears it again.
  * Results are identical to fma_b200_continuous_count.
  */
 int fma_b200_continuous_count_static(const void* ids, int32_t id_bytes, int64_t n, int32_t size, uint32_t* out,

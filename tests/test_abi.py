@@ -51,7 +51,7 @@ def test_status_strings_and_bad_arguments_without_gpu():
         _native.call("fma_b200_swiglu_forward", null, 8, null, 8, null, 8, 1, 4, 12, null)  # cols % 8
     assert lib.fma_b200_moe_rows_cap(1000, 8, 128) == 2048
     assert lib.fma_b200_moe_rows_cap(0, 1, 128) == 128
-    assert lib.fma_b200_continuous_count_workspace_bytes(128) >= 128 + 128 * 4
+    assert lib.fma_b200_continuous_count_workspace_bytes(128) == 128 + 8 * 128 * 4
 
 
 def test_python_surface_matches_reference_names():
