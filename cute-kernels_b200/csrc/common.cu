@@ -63,7 +63,7 @@ const char* fma_b200_status_string(int status) {
 
 const char* fma_b200_last_error(void) { return fmab::last_error_buffer(); }
 
-int fma_b200_abi_version(void) { return 1; }
+int fma_b200_abi_version(void) { return 2; }
 
 int fma_b200_device_status(int32_t* status_out, void* stream) {
     FMAB_REQUIRE(status_out != nullptr, FMA_B200_ERR_BAD_ARG, "status_out is NULL");

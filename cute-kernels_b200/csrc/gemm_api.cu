@@ -1,5 +1,7 @@
 // C-ABI entry points of the grouped GEMMs: argument checks and dtype dispatch
 // (bf16 -> tcgen05 kernel, f32 -> FFMA kernel).
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace fmab {
@@ -14,12 +16,36 @@ int tc_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, i
 int tc_general(const void* A, const void* B, void* D, const uint32_t* M, const uint32_t* N, const uint32_t* K,
                int n_groups, bool a_t, bool b_t, void* workspace, int64_t workspace_bytes, cudaStream_t s);
 int64_t tc_general_workspace_bytes(int n_groups, int64_t total_mtiles);
+int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
+                const int32_t* mtile_expert, cudaStream_t s);
+int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
+                       const int32_t* mtile_expert, cudaStream_t s);
+int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
+              const int32_t* mtile_expert, bool swiglu, cudaStream_t s);
+int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
+              const int32_t* seg_offsets, int n_seg, cudaStream_t s);
 int simt_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
                  const int32_t* mtile_expert, cudaStream_t s);
 int simt_dgrad(const void* dY, const void* W, void* dX, int64_t rows_cap, int E, int OUT, int IN,
                const int32_t* mtile_expert, cudaStream_t s);
 int simt_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
                const int32_t* seg_offsets, int n_seg, cudaStream_t s);
+
+// CTA-pair kernels (cta_group::2) are used when the grouped rows are aligned to 256; FMA_B200_GEMM_PAIRS=0
+// forces the single-CTA kernels (a measurement knob).
+static bool use_pairs(int32_t row_align) {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* env = getenv("FMA_B200_GEMM_PAIRS");
+        enabled = (env != nullptr && atoi(env) == 0) ? 0 : 1;
+    }
+    return enabled == 1 && row_align > 0 && row_align % 256 == 0;
+}
+
+static bool pairs_for_fused_epilogues() {
+    const char* env = getenv("FMA_B200_GEMM_PAIRS");
+    return env != nullptr && atoi(env) == 2;
+}
 
 static int check_layer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN) {
     FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
@@ -36,25 +62,28 @@ static int check_layer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t 
 extern "C" {
 
 int fma_b200_moe_gemm_forward(const void* X, const void* W, void* Y, int32_t dtype, int64_t rows_cap, int32_t E,
-                              int32_t OUT, int32_t IN, const int32_t* mtile_expert, void* stream) {
+                              int32_t OUT, int32_t IN, const int32_t* mtile_expert, int32_t row_align, void* stream) {
     using namespace fmab;
     if (int rc = check_layer_gemm(dtype, rows_cap, E, OUT, IN)) return rc;
     if (rows_cap == 0) return FMA_B200_OK;
     FMAB_REQUIRE(X && W && Y && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(X) && aligned16(W) && aligned16(Y), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == FMA_B200_BF16 && use_pairs(row_align)) return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
     if (dtype == FMA_B200_BF16) return tc_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
     return simt_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
 }
 
 int fma_b200_moe_gemm_dgrad(const void* dY, const void* W, void* dX, int32_t dtype, int64_t rows_cap, int32_t E,
-                            int32_t OUT, int32_t IN, const int32_t* mtile_expert, void* stream) {
+                            int32_t OUT, int32_t IN, const int32_t* mtile_expert, int32_t row_align, void* stream) {
     using namespace fmab;
     if (int rc = check_layer_gemm(dtype, rows_cap, E, OUT, IN)) return rc;
     if (rows_cap == 0) return FMA_B200_OK;
     FMAB_REQUIRE(dY && W && dX && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(dX), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == FMA_B200_BF16 && use_pairs(row_align))
+        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, s);
     if (dtype == FMA_B200_BF16) return tc_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, s);
     return simt_dgrad(dY, W, dX, rows_cap, E, OUT, IN, mtile_expert, s);
 }
@@ -68,13 +97,14 @@ int fma_b200_moe_gemm_wgrad(const void* dY, const void* X, void* dW, int32_t dty
     FMAB_REQUIRE(rows_cap > 0 && dY && X, FMA_B200_ERR_BAD_ARG, "wgrad needs non-empty dY and X buffers");
     FMAB_REQUIRE(aligned16(dY) && aligned16(X) && aligned16(dW), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == FMA_B200_BF16 && use_pairs(256)) return tc2_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, s);
     if (dtype == FMA_B200_BF16) return tc_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, s);
     return simt_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, s);
 }
 
 int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, void* act, int32_t dtype,
                                      int64_t rows_cap, int32_t E, int32_t I, int32_t IN, const int32_t* mtile_expert,
-                                     void* stream) {
+                                     int32_t row_align, void* stream) {
     using namespace fmab;
     FMAB_REQUIRE(dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED,
                  "the SwiGLU-fused up projection exists for bf16 only; run forward + swiglu_forward for f32");
@@ -84,12 +114,16 @@ int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, vo
     FMAB_REQUIRE(X && W && act && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(X) && aligned16(W) && aligned16(act) && aligned16(pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
+    // The SwiGLU epilogues are long; they run on the single-CTA kernel, whose two accumulators belong to
+    // different tiles so that an epilogue overlaps the next tile's main loop (FMA_B200_GEMM_PAIRS=2 forces pairs).
+    if (use_pairs(row_align) && pairs_for_fused_epilogues())
+        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, static_cast<cudaStream_t>(stream));
     return tc_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, static_cast<cudaStream_t>(stream));
 }
 
 int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pre, void* d_pre, int32_t dtype,
                                    int64_t rows_cap, int32_t E, int32_t OUT, int32_t I, const int32_t* mtile_expert,
-                                   void* stream) {
+                                   int32_t row_align, void* stream) {
     using namespace fmab;
     FMAB_REQUIRE(dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED,
                  "the SwiGLU-fused dgrad exists for bf16 only; run dgrad + swiglu_backward for f32");
@@ -98,6 +132,8 @@ int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pr
     FMAB_REQUIRE(dY && W && pre && d_pre && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(pre) && aligned16(d_pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
+    if (use_pairs(row_align) && pairs_for_fused_epilogues())
+        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, static_cast<cudaStream_t>(stream));
     return tc_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, static_cast<cudaStream_t>(stream));
 }
 

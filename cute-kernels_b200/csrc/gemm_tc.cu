@@ -19,192 +19,11 @@
 //
 // Every mbarrier wait is bounded (about one second of %globaltimer); a wait that runs out sets
 // the device status word, raises a CTA-wide abort flag that all other waits poll, and the CTA
-// leaves through the normal teardown (tensor memory is released).
-#include <cuda.h>
-#include <stdlib.h>
-
 #include <vector>
 
-#include "common.cuh"
+#include "gemm_tc.cuh"
 
 namespace fmab {
-
-// ---------------------------------------------------------------------------
-// tile shape
-// ---------------------------------------------------------------------------
-constexpr int BM = 128;           // rows of D per tile = TMEM lanes
-constexpr int BN = 256;           // columns of D per tile = TMEM columns per accumulator
-constexpr int BK = 64;            // reduction elements per stage = one 128-byte swizzle row of bf16
-constexpr int UMMA_K = 16;        // reduction elements per tcgen05.mma (bf16)
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int B_STAGE_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int MAX_GEMM_THREADS = 320;  // 2 + 8 warps; the 4-epilogue-warp build uses 192
-constexpr int TMEM_COLS = 512;
-constexpr int SUPER_M = 16;       // m-tiles walked together so that concurrent CTAs share operand tiles in L2
-constexpr size_t GEMM_SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;
-
-constexpr int EPI_PLAIN = 0;
-constexpr int EPI_SWIGLU_FWD = 1;
-constexpr int EPI_SWIGLU_BWD = 2;
-
-constexpr int MODE_ROWS = 0;     // ragged M: m-tile -> expert through mtile_expert (forward, dgrad)
-constexpr int MODE_WGRAD = 1;    // ragged K: tile = (expert, m-tile, n-tile), k runs over the expert's rows
-constexpr int MODE_GENERAL = 2;  // per-group tensor maps and host-built tables
-
-constexpr int32_t STATUS_GEMM_TIMEOUT = 0x7001;
-
-// Tables of the general mode (host-built, in the caller's workspace).
-struct GroupRec {
-    int32_t m, n, k;      // problem size of the group
-    int32_t first_mtile;  // index of its first m-tile
-    int64_t d_offset;     // element offset of D_g in the packed output
-};
-struct MTileRec {
-    int32_t group;
-    int32_t row0;  // first row of the tile inside the group
-};
-
-struct GemmParams {
-    CUtensorMap map_a;
-    CUtensorMap map_b;
-    const CUtensorMap* group_maps;  // general mode: [2g] = A_g, [2g+1] = B_g
-    const GroupRec* groups;
-    const MTileRec* mtiles;
-    const int32_t* mtile_expert;  // rows mode
-    const int32_t* seg_offsets;   // wgrad mode: [n_seg][E] (+1)
-    __nv_bfloat16* d;             // output (act for SWIGLU_FWD, d_pre for SWIGLU_BWD)
-    __nv_bfloat16* d2;            // SWIGLU_FWD: pre (may be null)
-    const __nv_bfloat16* pre;     // SWIGLU_BWD: saved pre-activations
-    int32_t* status;
-    int64_t ldd;                  // row pitch of d in elements
-    int32_t mode;
-    int32_t n_mtiles;             // m-tiles to walk
-    int32_t n_ntiles;
-    int32_t m_per_group;          // wgrad: rows of D per expert (OUT)
-    int32_t mtiles_per_group;     // wgrad: ceil(OUT / 128)
-    int32_t n_cols;               // columns of D (rows/wgrad modes)
-    int32_t k_len;                // rows mode: reduction length
-    int32_t b_group_stride;       // rows mode: B coordinate step per expert (rows of the stacked weight)
-    int32_t n_groups;             // E
-    int32_t n_seg;                // wgrad: segments per expert
-    int32_t inter;                // SwiGLU: intermediate size I
-};
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ uint64_t global_timer() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false if the wait was given up (here or by another thread of the CTA).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer();
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_timer() - t0 > 1000000000ull) {  // one second
-            *abort_flag = 1;
-            atomicExch(status, STATUS_GEMM_TIMEOUT);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void tensormap_acquire(const CUtensorMap* map) {
-    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives row (lane base + i).
-__device__ __forceinline__ void tc_load_32(uint32_t taddr, float* v) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile.
-//   K-major : rows of 64 bf16 (128 B); 8-row groups 1024 B apart (stride byte offset).
-//   MN-major: rows of 64 MN elements (128 B) per k; 8-k groups 1024 B apart (stride byte offset);
-//             the next 64 MN elements start BK*128 B further (leading byte offset).
-template <bool MN_MAJOR>
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    constexpr uint64_t lbo = MN_MAJOR ? (BK * 128) >> 4 : 1;
-    constexpr uint64_t sbo = 1024 >> 4;
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);  // start address, bits [0,14)
-    d |= lbo << 16;                                           // leading byte offset, bits [16,30)
-    d |= sbo << 32;                                           // stride byte offset, bits [32,46)
-    d |= 1ull << 46;                                          // descriptor version for sm_100
-    d |= 2ull << 61;                                          // layout: 128-byte swizzle
-    return d;
-}
-// Bytes to advance the start address for the next 16 reduction elements.
-template <bool MN_MAJOR>
-__device__ __forceinline__ constexpr uint32_t desc_k_step() { return MN_MAJOR ? UMMA_K * 128 : UMMA_K * 2; }
-
-template <bool A_MN, bool B_MN>
-__device__ __forceinline__ constexpr uint32_t make_instr_desc() {
-    return (1u << 4)                      // accumulator format: fp32
-           | (1u << 7)                    // A format: bf16
-           | (1u << 10)                   // B format: bf16
-           | ((A_MN ? 1u : 0u) << 15)     // A major
-           | ((B_MN ? 1u : 0u) << 16)     // B major
-           | (static_cast<uint32_t>(BN >> 3) << 17)
-           | (static_cast<uint32_t>(BM >> 4) << 24);
-}
 
 // ---------------------------------------------------------------------------
 // tile decode (identical in all three roles)
@@ -312,27 +131,6 @@ __device__ __forceinline__ void decode_segment(const GemmParams& p, const Tile& 
 }
 
 // ---------------------------------------------------------------------------
-// epilogue helpers: one thread owns one output row, 32 columns at a time
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float* v, int cols_left) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (q * 8 < cols_left) st_global_16(dst + q * 8, Elem<__nv_bfloat16>::pack(v + q * 8));
-    }
-}
-__device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float* v, int cols_left) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (q * 8 < cols_left) {
-            Elem<__nv_bfloat16>::unpack(ld_global_16(src + q * 8), v + q * 8);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[q * 8 + i] = 0.f;
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
 template <bool A_MN, bool B_MN, int EPI, int EPI_WARPS>
@@ -342,6 +140,10 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
     __shared__ __align__(8) uint64_t acc_full_bar[2];
     __shared__ __align__(8) uint64_t acc_empty_bar[2];
+    __shared__ __align__(8) uint64_t sched_full_bar[SCHED_SLOTS];
+    __shared__ __align__(8) uint64_t sched_empty_bar[SCHED_SLOTS];
+    __shared__ volatile int sched_tile[SCHED_SLOTS];
+    __shared__ volatile int sched_expert[SCHED_SLOTS];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -358,6 +160,10 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&acc_full_bar[b]), 1);
             mbar_init(smem_u32(&acc_empty_bar[b]), EPI_WARPS);  // one arrival per epilogue warp
+        }
+        for (int i = 0; i < SCHED_SLOTS; ++i) {
+            mbar_init(smem_u32(&sched_full_bar[i]), 1);
+            mbar_init(smem_u32(&sched_empty_bar[i]), 1 + EPI_WARPS);  // MMA thread + every epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -383,52 +189,74 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
-            int e_next = peek_expert(p, blockIdx.x, total_tiles);
-            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-                Tile t;
-                const int e_cur = e_next;
-                e_next = peek_expert(p, tile + gridDim.x, total_tiles);
-                if (!decode_tile<B_MN, EPI>(p, tile, e_cur, t)) continue;
-                if (p.mode == MODE_GENERAL) {
-                    tensormap_acquire(t.map_a);
-                    tensormap_acquire(t.map_b);
+            // This thread is also the tile scheduler: tiles are handed out by a global counter (the first
+            // one is blockIdx.x), so CTAs that start late or draw long tiles simply take fewer of them.
+            int sslot = 0;
+            uint32_t sphase = 0;
+            int tile = blockIdx.x;
+            int e_cur = peek_expert(p, tile, total_tiles);
+            while (alive) {
+                if (!mbar_wait(smem_u32(&sched_empty_bar[sslot]), sphase ^ 1u, abort_ptr, p.status)) {
+                    alive = false;
+                    break;
                 }
-                for (int s = 0; s < n_seg && alive; ++s) {
-                    int a_k0, b_k0, len;
-                    decode_segment(p, t, s, a_k0, b_k0, len);
-                    for (int k = 0; k < len; k += BK) {
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr, p.status)) {
-                            alive = false;
-                            break;
-                        }
-                        const uint32_t bar = smem_u32(&full_bar[stage]);
-                        const uint32_t sa = ring + stage * STAGE_BYTES;
-                        const uint32_t sb = sa + A_STAGE_BYTES;
-                        mbar_arrive_expect_tx(bar, STAGE_BYTES);
-                        if (A_MN) {
+                const bool end = tile >= total_tiles;
+                sched_tile[sslot] = end ? -1 : tile;
+                sched_expert[sslot] = e_cur;
+                mbar_arrive(smem_u32(&sched_full_bar[sslot]));  // release: the two stores above are visible to waiters
+                if (++sslot == SCHED_SLOTS) {
+                    sslot = 0;
+                    sphase ^= 1u;
+                }
+                if (end) break;
+                // drawn now, needed only after this tile's loads have been issued
+                const int next = p.dynamic_tiles ? static_cast<int>(atomicAdd(p.sched, 1u)) + static_cast<int>(gridDim.x)
+                                                 : tile + static_cast<int>(gridDim.x);
+                Tile t;
+                if (decode_tile<B_MN, EPI>(p, tile, e_cur, t)) {
+                    if (p.mode == MODE_GENERAL) {
+                        tensormap_acquire(t.map_a);
+                        tensormap_acquire(t.map_b);
+                    }
+                    for (int s = 0; s < n_seg && alive; ++s) {
+                        int a_k0, b_k0, len;
+                        decode_segment(p, t, s, a_k0, b_k0, len);
+                        for (int k = 0; k < len; k += BK) {
+                            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr, p.status)) {
+                                alive = false;
+                                break;
+                            }
+                            const uint32_t bar = smem_u32(&full_bar[stage]);
+                            const uint32_t sa = ring + stage * STAGE_BYTES;
+                            const uint32_t sb = sa + A_STAGE_BYTES;
+                            mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                            if (A_MN) {
 #pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_2d(sa + j * (BK * 128), t.map_a, bar, t.a_mn + 64 * j, a_k0 + k);
-                        } else {
-                            tma_load_2d(sa, t.map_a, bar, a_k0 + k, t.a_mn);
-                        }
-                        if (B_MN) {
+                                for (int j = 0; j < BM / 64; ++j)
+                                    tma_load_2d(sa + j * (BK * 128), t.map_a, bar, t.a_mn + 64 * j, a_k0 + k);
+                            } else {
+                                tma_load_2d(sa, t.map_a, bar, a_k0 + k, t.a_mn);
+                            }
+                            if (B_MN) {
 #pragma unroll
-                            for (int j = 0; j < BN / 64; ++j)
-                                tma_load_2d(sb + j * (BK * 128), t.map_b, bar, t.b_mn + 64 * j, b_k0 + k);
-                        } else if (EPI == EPI_SWIGLU_FWD) {
-                            // up rows n0.. and gate rows I+n0.. of the same expert, 128 each
-                            tma_load_2d(sb, t.map_b, bar, b_k0 + k, t.b_mn);
-                            tma_load_2d(sb + (BN / 2) * (BK * 2), t.map_b, bar, b_k0 + k, t.b_mn + p.inter);
-                        } else {
-                            tma_load_2d(sb, t.map_b, bar, b_k0 + k, t.b_mn);
-                        }
-                        if (++stage == STAGES) {
-                            stage = 0;
-                            phase ^= 1u;
+                                for (int j = 0; j < BN / 64; ++j)
+                                    tma_load_2d(sb + j * (BK * 128), t.map_b, bar, t.b_mn + 64 * j, b_k0 + k);
+                            } else if (EPI == EPI_SWIGLU_FWD) {
+                                // up rows n0.. and gate rows I+n0.. of the same expert, 128 each
+                                tma_load_2d(sb, t.map_b, bar, b_k0 + k, t.b_mn);
+                                tma_load_2d(sb + (BN / 2) * (BK * 2), t.map_b, bar, b_k0 + k, t.b_mn + p.inter);
+                            } else {
+                                tma_load_2d(sb, t.map_b, bar, b_k0 + k, t.b_mn);
+                            }
+                            if (++stage == STAGES) {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
                         }
                     }
                 }
+                tile = next;
+                e_cur = peek_expert(p, tile, total_tiles);
             }
             if (!alive) {
                 // give copies that are still in flight time to land before the CTA retires
@@ -444,11 +272,19 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
             int buf = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
-            int e_next = peek_expert(p, blockIdx.x, total_tiles);
-            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+            int sslot = 0;
+            uint32_t sphase = 0;
+            while (alive) {
+                if (!mbar_wait(smem_u32(&sched_full_bar[sslot]), sphase, abort_ptr, p.status)) break;
+                const int tile = sched_tile[sslot];
+                const int e_cur = sched_expert[sslot];
+                mbar_arrive(smem_u32(&sched_empty_bar[sslot]));
+                if (++sslot == SCHED_SLOTS) {
+                    sslot = 0;
+                    sphase ^= 1u;
+                }
+                if (tile < 0) break;
                 Tile t;
-                const int e_cur = e_next;
-                e_next = peek_expert(p, tile + gridDim.x, total_tiles);
                 if (!decode_tile<B_MN, EPI>(p, tile, e_cur, t)) continue;
                 if (!mbar_wait(smem_u32(&acc_empty_bar[buf]), acc_phase ^ 1u, abort_ptr, p.status)) break;
                 tc_fence_after();
@@ -497,11 +333,20 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
         const int row_in_tile = quad * 32 + lane;
         int buf = 0;
         uint32_t acc_phase = 0;
-        int e_next = peek_expert(p, blockIdx.x, total_tiles);
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int sslot = 0;
+        uint32_t sphase = 0;
+        while (true) {
+            if (!mbar_wait(smem_u32(&sched_full_bar[sslot]), sphase, abort_ptr, p.status)) break;
+            const int tile = sched_tile[sslot];
+            const int e_cur = sched_expert[sslot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sched_empty_bar[sslot]));
+            if (++sslot == SCHED_SLOTS) {
+                sslot = 0;
+                sphase ^= 1u;
+            }
+            if (tile < 0) break;
             Tile t;
-            const int e_cur = e_next;
-            e_next = peek_expert(p, tile + gridDim.x, total_tiles);
             if (!decode_tile<B_MN, EPI>(p, tile, e_cur, t)) continue;
             // Does this tile have any reduction work?  (Same test as the MMA issuer's.)
             bool any_k = false;
@@ -619,48 +464,17 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
-}
-
-// ---------------------------------------------------------------------------
-// host side: tensor maps and launches
-// ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    if (threadIdx.x == 0) {
+        // the last CTA to leave puts the scheduler words back to zero for the next launch that uses them
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+            p.sched[0] = 0;
+            p.sched[1] = 0;
+            __threadfence();
+        }
     }
-    return fn;
 }
 
-// 2-D bf16 tensor [outer, inner] with row pitch `pitch` elements, box [box_outer, box_inner], 128-byte swizzle.
-static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
-                     uint32_t box_inner, uint32_t box_outer) {
-    EncodeTiledFn fn = encode_fn();
-    FMAB_REQUIRE(fn != nullptr, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
-    FMAB_REQUIRE(aligned16(base), FMA_B200_ERR_BAD_ARG, "GEMM operand is not 16-byte aligned");
-    FMAB_REQUIRE((pitch * 2) % 16 == 0, FMA_B200_ERR_BAD_ARG, "row pitch %llu elements is not a multiple of 8",
-                 (unsigned long long)pitch);
-    FMAB_REQUIRE(inner >= 1 && outer >= 1, FMA_B200_ERR_BAD_ARG, "empty tensor for a tensor map");
-    const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {pitch * 2};
-    const cuuint32_t box[2] = {box_inner, box_outer};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    FMAB_REQUIRE(r == CUDA_SUCCESS, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    return FMA_B200_OK;
-}
-
-// Epilogue width: 8 warps (two per TMEM lane quadrant) by default; FMA_B200_GEMM_EPI_WARPS=4 selects
 // the narrower build (a tuning knob for measurements).
 static int epilogue_warps() {
     static int cached = 0;
@@ -671,8 +485,36 @@ static int epilogue_warps() {
     return cached;
 }
 
+// Scheduler words of the dynamic tile scheduler: 64 pairs per device, handed out round-robin so that
+// launches running concurrently on different streams do not share a pair.  Zero at load; every launch
+// leaves its pair zero again.
+static __device__ unsigned int g_sched_words[64 * 2];
+
+static int next_sched_pair(unsigned int** out) {
+    static unsigned int* base[64] = {nullptr};
+    static unsigned int seq = 0;
+    int dev = -1;
+    FMAB_CUDA(cudaGetDevice(&dev));
+    FMAB_REQUIRE(dev >= 0 && dev < 64, FMA_B200_ERR_BAD_ARG, "device ordinal %d is outside [0,64)", dev);
+    if (base[dev] == nullptr) {
+        void* ptr = nullptr;
+        FMAB_CUDA(cudaGetSymbolAddress(&ptr, g_sched_words));
+        base[dev] = static_cast<unsigned int*>(ptr);
+    }
+    *out = base[dev] + 2 * (__atomic_fetch_add(&seq, 1u, __ATOMIC_RELAXED) % 64u);
+    return FMA_B200_OK;
+}
+
 template <bool A_MN, bool B_MN, int EPI, int EPI_WARPS>
-static int launch_gemm_w(const GemmParams& p, cudaStream_t s) {
+static int launch_gemm_w(const GemmParams& p_in, cudaStream_t s) {
+    GemmParams p = p_in;
+    if (int rc = next_sched_pair(&p.sched)) return rc;
+    static int dynamic = -1;  // FMA_B200_GEMM_STATIC_TILES=1 switches the dynamic tile scheduler off (measurement knob)
+    if (dynamic < 0) {
+        const char* env = getenv("FMA_B200_GEMM_STATIC_TILES");
+        dynamic = (env != nullptr && atoi(env) == 1) ? 0 : 1;
+    }
+    p.dynamic_tiles = dynamic;
     static bool configured = false;
     auto kernel = gemm_tc_kernel<A_MN, B_MN, EPI, EPI_WARPS>;
     if (!configured) {

@@ -1,0 +1,576 @@
+// bf16 grouped GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256x512 output tile per pair of SMs.
+//
+// Why pairs: a 128x256x16 MMA issued by one CTA reads 12 KB of shared memory per 128 tensor-pipe
+// cycles while TMA writes the next operands at the same rate, which together exceed what the
+// shared-memory port delivers; the tensor pipe then idles about a third of the time.  With
+// cta_group::2 the two CTAs of a cluster each hold their own 128 rows of A and HALF of the B tile
+// (128 of the 256 columns); the pair's tensor cores use both halves, so every SM stages 32 KB per
+// k-block instead of 48 KB and reads a third less per MMA.
+//
+// The kernels are bound by the bytes that cross from L2 to the SMs (measured ceiling ~9.2 TB/s), so a
+// pair tile is 256 rows x 512 columns: per k-block each CTA loads its 128x64 slab of A ONCE and two
+// 128-column slabs of B, and the leader issues two MMAs per k-step into the two 256-column halves of
+// tensor memory.  That is 96 KB of loads per 16.8 MFLOP instead of 128 KB.  The halves have their own
+// full/empty barriers, so the epilogue of half 0 overlaps the MMAs of half 1 and the next tile may
+// start on half 0 while half 1 is still being stored.
+//
+// Structure (both CTAs run the same code; "leader" = cluster rank 0):
+//   warp 0      TMA producer in each CTA: loads its A slab and its B slabs into a 4-stage ring.
+//               All loads of a stage signal ONE mbarrier, the leader's (its address taken with
+//               mapa); the leader arms it with the byte count of both CTAs.
+//   warp 1      leader only: issues tcgen05.mma.cta_group::2 (M=256, N=256, K=16) and releases ring
+//               stages / publishes accumulators with tcgen05.commit on both CTAs' barriers.
+//   warps 2-9   epilogue in each CTA for its own 128 rows (tensor memory lanes), as in the
+//               single-CTA kernel; they free an accumulator by arriving on the leader's barrier.
+// Tiles are assigned statically to pairs (pair p takes tiles p, p + pairs, ...), so the two CTAs
+// need no scheduling traffic.  Loads are the plain per-CTA cp.async.bulk.tensor form with the
+// cta_group::2 qualifier; nothing in this file broadcasts a load to several CTAs.
+// Token rows must be grouped with 256-row alignment so that both CTAs of a pair work for the same
+// expert (forward / dgrad); wgrad pairs two 128-row slabs of one expert's weight gradient.
+// Every mbarrier wait is bounded as in the single-CTA kernel; both CTAs always reach the final
+// cluster barrier.
+#include "gemm_tc.cuh"
+
+namespace fmab {
+
+constexpr int PAIR_STAGES = 4;
+constexpr int PAIR_HALVES = 2;                                      // 256-column accumulator halves per tile
+constexpr int PAIR_B_ROWS = BN / 2;                                 // B rows staged per CTA and half (128)
+constexpr int PAIR_B_BYTES = PAIR_B_ROWS * BK * 2;                  // 16 KB
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_HALVES * PAIR_B_BYTES;  // 16 KB + 2 x 16 KB
+constexpr int PAIR_THREADS = 320;
+constexpr int PAIR_EPI_WARPS = 8;
+constexpr size_t PAIR_SMEM_BYTES = static_cast<size_t>(PAIR_STAGES) * PAIR_STAGE_BYTES + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on the LEADER's mbarrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives (once the MMAs issued so far have completed) on the barrier at this offset in BOTH CTAs:
+// one commit on the leader's own barrier, one on the peer's (its shared::cluster address).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    const uint32_t peer_bar = map_to_rank(bar, 1);
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer_bar) : "memory");
+}
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ constexpr uint32_t make_instr_desc_pair() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>((2 * BM) >> 4) << 24);  // M = 256
+}
+
+// Work of one CTA for one pair tile.
+struct PairTile {
+    int32_t group;
+    int32_t a_mn;      // this CTA's A coordinate along M
+    int32_t b_mn;      // this CTA's B coordinate along N (its half of the tile's columns)
+    int32_t b_k_base;
+    int32_t n0;          // first D column of half 0
+    int32_t n_step;      // D columns per half (256, or 128 act columns with the SwiGLU epilogue)
+    int32_t halves;      // 1 or 2 halves carry columns
+    int32_t rows_valid;
+    int64_t d_row;
+};
+
+// tile -> (pair m-tile, n-tile) with SUPER_M/2 pair m-tiles walked together
+template <bool B_MN, int EPI>
+__device__ __forceinline__ bool decode_pair_tile(const GemmParams& p, int tile, int n_pair_mtiles, uint32_t rank, PairTile& t) {
+    constexpr int kSuper = SUPER_M / 2;
+    const int per_super = kSuper * p.n_ntiles;
+    const int super = tile / per_super;
+    const int m_first = super * kSuper;
+    const int m_span = min(kSuper, n_pair_mtiles - m_first);
+    const int r = tile - super * per_super;
+    const int nt = r / m_span;
+    const int pm = m_first + (r - nt * m_span);
+    constexpr int n_step = (EPI == EPI_SWIGLU_FWD) ? BN / 2 : BN;
+    t.n0 = nt * PAIR_HALVES * n_step;
+    t.n_step = n_step;
+    t.halves = (t.n0 + n_step < p.n_cols) ? 2 : 1;
+    t.b_k_base = 0;
+    if (p.mode == MODE_ROWS) {
+        const int e = __ldg(p.mtile_expert + 2 * pm);  // both 128-row tiles of the pair belong to this expert
+        if (e < 0) return false;
+        const int mt = 2 * pm + static_cast<int>(rank);
+        t.group = e;
+        t.a_mn = mt * BM;
+        t.d_row = static_cast<int64_t>(mt) * BM;
+        t.rows_valid = (mt < p.n_mtiles) ? BM : 0;
+        if (EPI == EPI_SWIGLU_FWD) {
+            // leader stages the 128 up rows, the peer the 128 gate rows of the same act columns
+            t.b_mn = e * p.b_group_stride + t.n0 + static_cast<int>(rank) * p.inter;
+        } else if (B_MN) {
+            t.b_mn = t.n0 + static_cast<int>(rank) * PAIR_B_ROWS;
+            t.b_k_base = e * p.b_group_stride;
+        } else {
+            t.b_mn = e * p.b_group_stride + t.n0 + static_cast<int>(rank) * PAIR_B_ROWS;
+        }
+    } else {  // MODE_WGRAD: pair m-tiles are counted per expert
+        const int pairs_per_group = (p.mtiles_per_group + 1) / 2;
+        const int e = pm / pairs_per_group;
+        const int m0 = ((pm - e * pairs_per_group) * 2 + static_cast<int>(rank)) * BM;
+        t.group = e;
+        t.a_mn = m0;
+        t.b_mn = t.n0 + static_cast<int>(rank) * PAIR_B_ROWS;
+        t.d_row = static_cast<int64_t>(e) * p.m_per_group + m0;
+        t.rows_valid = max(0, min(BM, p.m_per_group - m0));
+    }
+    return true;
+}
+
+__device__ __forceinline__ void decode_pair_segment(const GemmParams& p, const PairTile& t, int s, int& a_k0, int& b_k0, int& len) {
+    if (p.mode == MODE_ROWS) {
+        a_k0 = 0;
+        b_k0 = t.b_k_base;
+        len = p.k_len;
+    } else {
+        const int32_t* o = p.seg_offsets + s * p.n_groups + t.group;
+        a_k0 = o[0];
+        b_k0 = o[0];
+        len = o[1] - o[0];
+    }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[PAIR_STAGES];   // used in the leader only
+    __shared__ __align__(8) uint64_t empty_bar[PAIR_STAGES];  // each CTA waits on its own copy
+    __shared__ __align__(8) uint64_t acc_full_bar[2];         // each CTA waits on its own copy
+    __shared__ __align__(8) uint64_t acc_empty_bar[2];        // used in the leader only
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full_bar[b]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[b]), 2 * PAIR_EPI_WARPS);  // every epilogue warp of both CTAs
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // the same warp of both CTAs takes part in the paired allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything is signalled across CTAs
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int* abort_ptr = &abort_flag;
+
+    const int n_pair_mtiles = (p.mode == MODE_ROWS) ? (p.n_mtiles + 1) / 2 : p.n_groups * ((p.mtiles_per_group + 1) / 2);
+    const int total_tiles = n_pair_mtiles * p.n_ntiles;
+    const int n_seg = (p.mode == MODE_WGRAD) ? p.n_seg : 1;
+    const int pair_id = blockIdx.x >> 1;
+    const int n_pairs = gridDim.x >> 1;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both CTAs) ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int tile = pair_id; tile < total_tiles && alive; tile += n_pairs) {
+                PairTile t;
+                if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+                for (int s = 0; s < n_seg && alive; ++s) {
+                    int a_k0, b_k0, len;
+                    decode_pair_segment(p, t, s, a_k0, b_k0, len);
+                    for (int k = 0; k < len; k += BK) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr, p.status)) {
+                            alive = false;
+                            break;
+                        }
+                        const uint32_t leader_bar = map_to_rank(smem_u32(&full_bar[stage]), 0);
+                        const uint32_t sa = ring + stage * PAIR_STAGE_BYTES;
+                        const uint32_t sb = sa + A_STAGE_BYTES;
+                        const uint32_t stage_bytes = A_STAGE_BYTES + t.halves * PAIR_B_BYTES;
+                        if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * stage_bytes);
+                        if (A_MN) {
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_2d_pair(sa + j * (BK * 128), &p.map_a, leader_bar, t.a_mn + 64 * j, a_k0 + k);
+                        } else {
+                            tma_load_2d_pair(sa, &p.map_a, leader_bar, a_k0 + k, t.a_mn);
+                        }
+                        for (int h = 0; h < t.halves; ++h) {
+                            const uint32_t sbh = sb + h * PAIR_B_BYTES;
+                            const int bn = t.b_mn + h * t.n_step;
+                            if (B_MN) {
+#pragma unroll
+                                for (int j = 0; j < PAIR_B_ROWS / 64; ++j)
+                                    tma_load_2d_pair(sbh + j * (BK * 128), &p.map_b, leader_bar, bn + 64 * j, b_k0 + k);
+                            } else {
+                                tma_load_2d_pair(sbh, &p.map_b, leader_bar, b_k0 + k, bn);
+                            }
+                        }
+                        if (++stage == PAIR_STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
+            }
+            if (!alive) {
+                for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = make_instr_desc_pair<A_MN, B_MN>();
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_phase = 0;
+            bool alive = true;
+            for (int tile = pair_id; tile < total_tiles && alive; tile += n_pairs) {
+                PairTile t;
+                if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+                // each half of tensor memory is free once both CTAs' epilogues have drained it
+                bool waited[PAIR_HALVES] = {false, false};
+                uint32_t accumulate = 0;
+                for (int s = 0; s < n_seg && alive; ++s) {
+                    int a_k0, b_k0, len;
+                    decode_pair_segment(p, t, s, a_k0, b_k0, len);
+                    for (int k = 0; k < len; k += BK) {
+                        if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_ptr, p.status)) {
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sa = ring + stage * PAIR_STAGE_BYTES;
+                        const uint32_t sb = sa + A_STAGE_BYTES;
+                        const uint64_t a_desc = make_smem_desc<A_MN>(sa);
+                        for (int h = 0; h < t.halves && alive; ++h) {
+                            if (!waited[h]) {
+                                if (!mbar_wait(smem_u32(&acc_empty_bar[h]), acc_phase ^ 1u, abort_ptr, p.status)) {
+                                    alive = false;
+                                    break;
+                                }
+                                tc_fence_after();
+                                waited[h] = true;
+                            }
+                            const uint64_t b_desc = make_smem_desc<B_MN>(sb + h * PAIR_B_BYTES);
+                            const uint32_t d_tmem = tmem_base + h * BN;
+#pragma unroll
+                            for (int ks = 0; ks < BK / UMMA_K; ++ks)
+                                tc_mma_pair(d_tmem, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
+                                            b_desc + ((ks * desc_k_step<B_MN>()) >> 4), idesc, (accumulate | ks) ? 1u : 0u);
+                        }
+                        if (!alive) break;
+                        accumulate = 1;
+                        tc_commit_pair(smem_u32(&empty_bar[stage]));  // frees the stage in both CTAs
+                        if (++stage == PAIR_STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
+                if (!alive) break;
+                for (int h = 0; h < t.halves; ++h) {
+                    if (accumulate) {
+                        tc_commit_pair(smem_u32(&acc_full_bar[h]));
+                    } else {  // empty reduction: both epilogues write zeros
+                        if (!mbar_wait(smem_u32(&acc_empty_bar[h]), acc_phase ^ 1u, abort_ptr, p.status)) {
+                            alive = false;
+                            break;
+                        }
+                        mbar_arrive(smem_u32(&acc_full_bar[h]));
+                        mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[h]), 1));
+                    }
+                }
+                if (t.halves == 1) {
+                    // keep half 1's barriers in step with the tile count: pass its phase through unused
+                    if (!mbar_wait(smem_u32(&acc_empty_bar[1]), acc_phase ^ 1u, abort_ptr, p.status)) break;
+                    mbar_arrive(smem_u32(&acc_full_bar[1]));
+                    mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[1]), 1));
+                }
+                acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (both CTAs, own 128 rows) ------------------------------
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int row_in_tile = quad * 32 + lane;
+        uint32_t acc_phase = 0;
+        for (int tile = pair_id; tile < total_tiles; tile += n_pairs) {
+            PairTile t;
+            if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+            bool any_k = false;
+            for (int s = 0; s < n_seg; ++s) {
+                int a_k0, b_k0, len;
+                decode_pair_segment(p, t, s, a_k0, b_k0, len);
+                any_k |= len > 0;
+            }
+            const bool row_ok = row_in_tile < t.rows_valid;
+            const int64_t grow = t.d_row + row_in_tile;
+            bool alive = true;
+            for (int h = 0; h < PAIR_HALVES; ++h) {
+            if (!mbar_wait(smem_u32(&acc_full_bar[h]), acc_phase, abort_ptr, p.status)) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + h * BN + (static_cast<uint32_t>(quad * 32) << 16);
+            const int n0h = t.n0 + h * t.n_step;                 // first D column of this half
+            const int n_valid = min(t.n_step, p.n_cols - n0h);   // <= 0: the half carries no columns
+
+            if (EPI == EPI_PLAIN) {
+                __nv_bfloat16* drow = p.d + grow * p.ldd + n0h;
+                constexpr int kChunks = BN / 32 / 2;
+#pragma unroll 1
+                for (int c = half * kChunks; c < (half + 1) * kChunks; ++c) {
+                    const int cols_left = n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    float v[32];
+                    if (any_k) {
+                        tc_load_32(taddr + c * 32, v);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                    }
+                    if (row_ok) store_row32_bf16(drow + c * 32, v, cols_left);
+                }
+            } else if (EPI == EPI_SWIGLU_FWD) {
+                __nv_bfloat16* arow = p.d + grow * p.ldd + n0h;
+                __nv_bfloat16* prow = p.d2 ? p.d2 + grow * (2 * static_cast<int64_t>(p.inter)) + n0h : nullptr;
+                constexpr int kChunks = BN / 64 / 2;
+#pragma unroll 1
+                for (int c = half * kChunks; c < (half + 1) * kChunks; ++c) {
+                    const int cols_left = n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    float u[32], g[32];
+                    tc_load_32(taddr + c * 32, u);
+                    tc_load_32(taddr + BN / 2 + c * 32, g);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        u[i] = round_bf16(u[i]);
+                        g[i] = round_bf16(g[i]);
+                    }
+                    if (row_ok && prow) {
+                        store_row32_bf16(prow + c * 32, u, cols_left);
+                        store_row32_bf16(prow + p.inter + c * 32, g, cols_left);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped(g[i]);
+                    if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
+                }
+            } else {
+                const __nv_bfloat16* prow = p.pre + grow * (2 * static_cast<int64_t>(p.inter)) + n0h;
+                __nv_bfloat16* drow = p.d + grow * (2 * static_cast<int64_t>(p.inter)) + n0h;
+                constexpr int kChunks = BN / 32 / 2;
+                const int c_begin = half * kChunks, c_end = (half + 1) * kChunks;
+                uint4 nu[4], ng[4];
+                auto fetch = [&](int c) {
+                    const int cols_left = n_valid - c * 32;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const bool ok = row_ok && q * 8 < cols_left;
+                        nu[q] = ok ? ld_global_16(prow + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
+                        ng[q] = ok ? ld_global_16(prow + p.inter + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
+                    }
+                };
+                fetch(c_begin);
+#pragma unroll 1
+                for (int c = c_begin; c < c_end; ++c) {
+                    const int cols_left = n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    float da[32], u[32], g[32];
+                    tc_load_32(taddr + c * 32, da);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        Elem<__nv_bfloat16>::unpack(nu[q], u + q * 8);
+                        Elem<__nv_bfloat16>::unpack(ng[q], g + q * 8);
+                    }
+                    if (c + 1 < c_end) fetch(c + 1);
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float d = round_bf16(da[i]);
+                            const float s = sigmoid_clamped(g[i]);
+                            const float silu = g[i] * s;
+                            da[i] = d * silu;
+                            g[i] = d * u[i] * (s + silu * (1.f - s));
+                        }
+                        store_row32_bf16(drow + c * 32, da, cols_left);
+                        store_row32_bf16(drow + p.inter + c * 32, g, cols_left);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty_bar[h]), 0));  // the leader's barrier
+            }  // halves
+            if (!alive) break;
+            acc_phase ^= 1u;
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA touches the pair's tensor memory or barriers after this point
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s) {
+    static bool configured = false;
+    auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI>;
+    if (!configured) {
+        FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM_BYTES));
+        configured = true;
+    }
+    if (total_tiles <= 0) return FMA_B200_OK;
+    FMAB_REQUIRE(total_tiles < (1LL << 31), FMA_B200_ERR_BAD_ARG, "too many tiles");
+    const int64_t max_pairs = sm_count() / 2;
+    const int pairs = static_cast<int>(total_tiles < max_pairs ? total_tiles : max_pairs);
+    kernel<<<2 * pairs, PAIR_THREADS, PAIR_SMEM_BYTES, s>>>(p);
+    return check_launch("grouped GEMM (tcgen05, CTA pairs)");
+}
+
+static int fill_pair_common(GemmParams& p) {
+    memset(&p, 0, sizeof(p));
+    p.status = device_status_ptr();
+    FMAB_REQUIRE(p.status != nullptr, FMA_B200_ERR_LAUNCH, "no device status word");
+    p.n_seg = 1;
+    return FMA_B200_OK;
+}
+
+int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
+                const int32_t* mtile_expert, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_pair_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, PAIR_B_ROWS)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.d = static_cast<__nv_bfloat16*>(Y);
+    p.ldd = OUT;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (OUT + 2 * BN - 1) / (2 * BN);
+    p.n_cols = OUT;
+    p.k_len = IN;
+    p.b_group_stride = OUT;
+    p.n_groups = E;
+    return launch_pair<false, false, EPI_PLAIN>(p, static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles, s);
+}
+
+int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
+                       const int32_t* mtile_expert, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_pair_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * 2 * I, IN, BK, PAIR_B_ROWS)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.d = static_cast<__nv_bfloat16*>(act);
+    p.d2 = static_cast<__nv_bfloat16*>(pre);
+    p.ldd = I;
+    p.inter = I;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (I + BN - 1) / BN;  // 2 halves of 128 act columns
+    p.n_cols = I;
+    p.k_len = IN;
+    p.b_group_stride = 2 * I;
+    p.n_groups = E;
+    return launch_pair<false, false, EPI_SWIGLU_FWD>(p, static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles, s);
+}
+
+int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
+              const int32_t* mtile_expert, bool swiglu, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_pair_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.d = static_cast<__nv_bfloat16*>(dX);
+    p.pre = static_cast<const __nv_bfloat16*>(pre);
+    p.ldd = swiglu ? 2 * static_cast<int64_t>(IN) : IN;
+    p.inter = IN;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (IN + 2 * BN - 1) / (2 * BN);
+    p.n_cols = IN;
+    p.k_len = OUT;
+    p.b_group_stride = OUT;
+    p.n_groups = E;
+    const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
+    if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD>(p, total, s);
+    return launch_pair<false, true, EPI_PLAIN>(p, total, s);
+}
+
+int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
+              const int32_t* seg_offsets, int n_seg, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_pair_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, 64, BK)) return rc;
+    if (int rc = encode_2d(&p.map_b, X, IN, rows_cap, IN, 64, BK)) return rc;
+    p.mode = MODE_WGRAD;
+    p.seg_offsets = seg_offsets;
+    p.n_seg = n_seg;
+    p.d = static_cast<__nv_bfloat16*>(dW);
+    p.ldd = IN;
+    p.m_per_group = OUT;
+    p.mtiles_per_group = (OUT + BM - 1) / BM;
+    p.n_mtiles = E * p.mtiles_per_group;
+    p.n_ntiles = (IN + 2 * BN - 1) / (2 * BN);
+    p.n_cols = IN;
+    p.n_groups = E;
+    const int64_t total = static_cast<int64_t>(E) * ((p.mtiles_per_group + 1) / 2) * p.n_ntiles;
+    return launch_pair<true, true, EPI_PLAIN>(p, total, s);
+}
+
+}  // namespace fmab

@@ -49,11 +49,11 @@ SIGNATURES: dict[str, tuple] = {
         ctypes.c_int,
         [_P, _I64, _P, _I64, _P, _I64, _P, _I64, _P, _I64, _I32, _I64, _I64, _P],
     ),
-    "fma_b200_moe_gemm_forward": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _P]),
-    "fma_b200_moe_gemm_dgrad": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _P]),
+    "fma_b200_moe_gemm_forward": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
+    "fma_b200_moe_gemm_dgrad": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
     "fma_b200_moe_gemm_wgrad": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
-    "fma_b200_moe_gemm_forward_swiglu": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _P]),
-    "fma_b200_moe_gemm_dgrad_swiglu": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _P]),
+    "fma_b200_moe_gemm_forward_swiglu": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
+    "fma_b200_moe_gemm_dgrad_swiglu": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
     "fma_b200_grouped_gemm_workspace_bytes": (_I64, [_I32, _I64]),
     "fma_b200_grouped_gemm": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _P, _I64, _P]),
 }

@@ -10,7 +10,7 @@ import torch
 from .. import _native
 from .._native import call, dtype_code, ptr, stream_ptr
 
-ROW_ALIGN = 128  # expert segments of the grouped layout start on 128-row tile boundaries
+ROW_ALIGN = 256  # expert segments start on 256-row boundaries: one tile of a CTA pair (128 rows per CTA)
 
 
 @dataclass
@@ -25,6 +25,7 @@ class RowMaps:
     rows_cap: int
     num_experts: int
     top_k: int
+    row_align: int = ROW_ALIGN
     sorted_expert_idxs: torch.Tensor | None = None  # int64 [R]
     sorted_scattered_idxs: torch.Tensor | None = None  # int64 [R]
 
@@ -71,7 +72,8 @@ def moe_sort(selected: torch.Tensor, E: int, *, want_sorted: bool = False, row_a
     call("fma_b200_moe_sort", ptr(selected), R, E, row_align, cap, ptr(sorted_e), ptr(sorted_s), ptr(expert_count),
          ptr(pad_offsets), ptr(row_of_slot), ptr(slot_of_row), ptr(mtile_expert), ptr(ws), ws_bytes,
          stream_ptr(dev))  # fmt: skip
-    return RowMaps(expert_count, pad_offsets, row_of_slot, slot_of_row, mtile_expert, cap, E, top_k, sorted_e, sorted_s)
+    return RowMaps(expert_count, pad_offsets, row_of_slot, slot_of_row, mtile_expert, cap, E, top_k, row_align, sorted_e,
+                   sorted_s)
 
 
 def scatter(x: torch.Tensor, maps: RowMaps) -> torch.Tensor:
@@ -109,21 +111,21 @@ def combine_backward(dy, expert_out, weights, maps: RowMaps, want_d_weights: boo
     return d_out, d_w
 
 
-def gemm_forward(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor) -> torch.Tensor:
+def gemm_forward(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor, row_align: int = ROW_ALIGN) -> torch.Tensor:
     E, OUT, IN = W.shape
     rows = X.size(0)
     Y = torch.empty(rows, OUT, dtype=X.dtype, device=X.device)
     call("fma_b200_moe_gemm_forward", ptr(X), ptr(W), ptr(Y), dtype_code(X.dtype), rows, E, OUT, IN,
-         ptr(mtile_expert), stream_ptr(X.device))  # fmt: skip
+         ptr(mtile_expert), row_align, stream_ptr(X.device))  # fmt: skip
     return Y
 
 
-def gemm_dgrad(dY: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor) -> torch.Tensor:
+def gemm_dgrad(dY: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor, row_align: int = ROW_ALIGN) -> torch.Tensor:
     E, OUT, IN = W.shape
     rows = dY.size(0)
     dX = torch.empty(rows, IN, dtype=dY.dtype, device=dY.device)
     call("fma_b200_moe_gemm_dgrad", ptr(dY), ptr(W), ptr(dX), dtype_code(dY.dtype), rows, E, OUT, IN,
-         ptr(mtile_expert), stream_ptr(dY.device))  # fmt: skip
+         ptr(mtile_expert), row_align, stream_ptr(dY.device))  # fmt: skip
     return dX
 
 
@@ -138,7 +140,8 @@ def gemm_wgrad(dY: torch.Tensor, X: torch.Tensor, E: int, seg_offsets: torch.Ten
     return dW
 
 
-def gemm_forward_swiglu(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor, keep_pre: bool = True):
+def gemm_forward_swiglu(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor, keep_pre: bool = True,
+                        row_align: int = ROW_ALIGN):
     """Up projection + SwiGLU.  bf16: one fused tcgen05 kernel; f32: GEMM then the swiglu kernel."""
     E, twoI, IN = W.shape
     I = twoI // 2
@@ -148,9 +151,9 @@ def gemm_forward_swiglu(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Te
         pre = torch.empty(rows, twoI, dtype=X.dtype, device=dev) if keep_pre else None
         act = torch.empty(rows, I, dtype=X.dtype, device=dev)
         call("fma_b200_moe_gemm_forward_swiglu", ptr(X), ptr(W), ptr(pre), ptr(act), dtype_code(X.dtype), rows, E, I,
-             IN, ptr(mtile_expert), stream_ptr(dev))  # fmt: skip
+             IN, ptr(mtile_expert), row_align, stream_ptr(dev))  # fmt: skip
         return pre, act
-    pre = gemm_forward(X, W, mtile_expert)
+    pre = gemm_forward(X, W, mtile_expert, row_align)
     act = torch.empty(rows, I, dtype=X.dtype, device=dev)
     up, gate = pre[:, :I], pre[:, I:]
     call("fma_b200_swiglu_forward", ptr(gate), twoI, ptr(up), twoI, ptr(act), I, dtype_code(X.dtype), rows, I,
@@ -158,7 +161,8 @@ def gemm_forward_swiglu(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Te
     return pre, act
 
 
-def gemm_dgrad_swiglu(d_out: torch.Tensor, W: torch.Tensor, pre: torch.Tensor, mtile_expert: torch.Tensor):
+def gemm_dgrad_swiglu(d_out: torch.Tensor, W: torch.Tensor, pre: torch.Tensor, mtile_expert: torch.Tensor,
+                      row_align: int = ROW_ALIGN):
     """d_pre [rows, 2I] from d_out [rows, H]: dgrad of the down projection + SwiGLU backward."""
     E, OUT, I = W.shape
     rows = d_out.size(0)
@@ -166,9 +170,9 @@ def gemm_dgrad_swiglu(d_out: torch.Tensor, W: torch.Tensor, pre: torch.Tensor, m
     d_pre = torch.empty(rows, 2 * I, dtype=d_out.dtype, device=dev)
     if d_out.dtype == torch.bfloat16:
         call("fma_b200_moe_gemm_dgrad_swiglu", ptr(d_out), ptr(W), ptr(pre), ptr(d_pre), dtype_code(d_out.dtype), rows,
-             E, OUT, I, ptr(mtile_expert), stream_ptr(dev))  # fmt: skip
+             E, OUT, I, ptr(mtile_expert), row_align, stream_ptr(dev))  # fmt: skip
         return d_pre
-    d_act = gemm_dgrad(d_out, W, mtile_expert)
+    d_act = gemm_dgrad(d_out, W, mtile_expert, row_align)
     up, gate = pre[:, :I], pre[:, I:]
     d_up, d_gate = d_pre[:, :I], d_pre[:, I:]
     call("fma_b200_swiglu_backward", ptr(gate), 2 * I, ptr(up), 2 * I, ptr(d_act), I, ptr(d_gate), 2 * I, ptr(d_up),

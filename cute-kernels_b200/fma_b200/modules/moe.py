@@ -5,7 +5,7 @@ kernels only.
 Data flow of `MoE.forward` (T tokens, R = T*k routed rows):
     logits = gate(x)                                  nn.Linear, kept as a replaceable module
     w, sel = top-k + softmax kernel                   [T,k]
-    maps   = stable counting sort of sel              expert segments padded to 128-row tiles
+    maps   = stable counting sort of sel              expert segments padded to 256-row tiles
     xg     = scatter(x)                               [rows_cap, H], padding rows zero
     pre, a = up-projection GEMM (+ SwiGLU epilogue)   tcgen05 for bf16, FFMA for f32
     out    = down-projection GEMM
@@ -65,14 +65,14 @@ class _ExpertLinear(torch.autograd.Function):
         weight = weight.contiguous()
         ctx.save_for_backward(x, weight)
         ctx.maps = maps
-        return K.gemm_forward(x, weight, maps.mtile_expert)
+        return K.gemm_forward(x, weight, maps.mtile_expert, maps.row_align)
 
     @staticmethod
     def backward(ctx, d_y):
         x, weight = ctx.saved_tensors
         maps = ctx.maps
         d_y = d_y.contiguous()
-        d_x = K.gemm_dgrad(d_y, weight, maps.mtile_expert) if ctx.needs_input_grad[0] else None
+        d_x = K.gemm_dgrad(d_y, weight, maps.mtile_expert, maps.row_align) if ctx.needs_input_grad[0] else None
         d_w = K.gemm_wgrad(d_y, x, weight.size(0), maps.pad_offsets) if ctx.needs_input_grad[1] else None
         return d_x, d_w, None
 
@@ -106,8 +106,8 @@ class _FusedSwigluExperts(torch.autograd.Function):
         w_proj = w_proj.contiguous()
         T = x.size(0)
         xg = K.scatter(x, maps)
-        pre, act = K.gemm_forward_swiglu(xg, w_fc, maps.mtile_expert, keep_pre=True)
-        out = K.gemm_forward(act, w_proj, maps.mtile_expert)
+        pre, act = K.gemm_forward_swiglu(xg, w_fc, maps.mtile_expert, keep_pre=True, row_align=maps.row_align)
+        out = K.gemm_forward(act, w_proj, maps.mtile_expert, maps.row_align)
         y = K.combine(out, weights, maps, T)
         ctx.save_for_backward(xg, pre, act, out, weights, w_fc, w_proj)
         ctx.maps = maps
@@ -124,11 +124,11 @@ class _FusedSwigluExperts(torch.autograd.Function):
         d_w_proj = K.gemm_wgrad(d_out, act, E, maps.pad_offsets) if need_proj else None
         d_x = d_w_fc = None
         if need_x or need_fc:
-            d_pre = K.gemm_dgrad_swiglu(d_out, w_proj, pre, maps.mtile_expert)
+            d_pre = K.gemm_dgrad_swiglu(d_out, w_proj, pre, maps.mtile_expert, maps.row_align)
             if need_fc:
                 d_w_fc = K.gemm_wgrad(d_pre, xg, E, maps.pad_offsets)
             if need_x:
-                d_xg = K.gemm_dgrad(d_pre, w_fc, maps.mtile_expert)
+                d_xg = K.gemm_dgrad(d_pre, w_fc, maps.mtile_expert, maps.row_align)
                 d_x = K.scatter_backward(d_xg, maps, ctx.T)
         return d_x, d_w, d_w_fc, d_w_proj, None
 

@@ -134,8 +134,8 @@ int fma_b200_router_topk_softmax_backward(const void* weights, const void* d_wei
  * (fma/modules/moe/cuda_implementation/__init__.py:83-104).
  *
  * Grouped layout: expert e owns rows [pad_offsets[e], pad_offsets[e+1]) where each
- * segment length is expert_count[e] rounded up to `row_align` (a multiple of 128,
- * or 1 for no padding); the first expert_count[e] rows of a segment hold its
+ * segment length is expert_count[e] rounded up to `row_align` (a multiple of 128 -
+ * 256 lets the GEMMs use CTA pairs - or 1 for no padding); the first expert_count[e] rows of a segment hold its
  * tokens in ascending flat index (t*k+j), the rest are padding.
  *
  * Outputs (any may be NULL to skip, except expert_count and pad_offsets):
@@ -254,11 +254,14 @@ int fma_b200_swiglu_backward(const void* gate, int64_t gate_pitch, const void* u
  * seg_offsets is then int32[n_seg*E+1] laid out [segment s][expert e] and
  * pad_offsets is ignored; pass n_seg = 1 and seg_offsets = pad_offsets otherwise.
  * IN and OUT must be multiples of 8; all pointers 16-byte aligned.
+ * row_align is the alignment the grouped rows were sorted with (fma_b200_moe_sort's row_align, or the
+ * one given to fma_b200_moe_ep_recv_maps): with a multiple of 256 the bf16 kernels run on CTA pairs
+ * (tcgen05 cta_group::2, one 256x256 tile per two SMs); with 128 on single CTAs (128x256 tiles).
  */
 int fma_b200_moe_gemm_forward(const void* X, const void* W, void* Y, int32_t dtype, int64_t rows_cap, int32_t E,
-                              int32_t OUT, int32_t IN, const int32_t* mtile_expert, void* stream);
+                              int32_t OUT, int32_t IN, const int32_t* mtile_expert, int32_t row_align, void* stream);
 int fma_b200_moe_gemm_dgrad(const void* dY, const void* W, void* dX, int32_t dtype, int64_t rows_cap, int32_t E,
-                            int32_t OUT, int32_t IN, const int32_t* mtile_expert, void* stream);
+                            int32_t OUT, int32_t IN, const int32_t* mtile_expert, int32_t row_align, void* stream);
 int fma_b200_moe_gemm_wgrad(const void* dY, const void* X, void* dW, int32_t dtype, int64_t rows_cap, int32_t E,
                             int32_t OUT, int32_t IN, const int32_t* seg_offsets, int32_t n_seg, void* stream);
 /*
@@ -271,7 +274,7 @@ int fma_b200_moe_gemm_wgrad(const void* dY, const void* X, void* dW, int32_t dty
  */
 int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, void* act, int32_t dtype,
                                      int64_t rows_cap, int32_t E, int32_t I, int32_t IN,
-                                     const int32_t* mtile_expert, void* stream);
+                                     const int32_t* mtile_expert, int32_t row_align, void* stream);
 /*
  * Down-projection dgrad with the SwiGLU backward in the epilogue:
  * d_act = dY . W[e] ([rows, I], rounded to dtype), then with up/gate read from pre
@@ -281,7 +284,7 @@ int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, vo
  */
 int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pre, void* d_pre, int32_t dtype,
                                    int64_t rows_cap, int32_t E, int32_t OUT, int32_t I,
-                                   const int32_t* mtile_expert, void* stream);
+                                   const int32_t* mtile_expert, int32_t row_align, void* stream);
 
 /*
  * General grouped GEMM with the reference's memory model: A, B and D are flat buffers of

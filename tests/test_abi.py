@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
         assert name in _native.SIGNATURES, f"{name} has no ctypes signature"
     assert sorted(_native.SIGNATURES) == names
-    assert lib.fma_b200_abi_version() == 1
+    assert lib.fma_b200_abi_version() == 2
 
 
 def test_status_strings_and_bad_arguments_without_gpu():
@@ -44,12 +44,13 @@ def test_status_strings_and_bad_arguments_without_gpu():
     assert b"NULL" in lib.fma_b200_last_error() or b"size" in lib.fma_b200_last_error()
     assert lib.fma_b200_continuous_count(null, 2, 0, 8, null, null, 0, null) == 1
     assert lib.fma_b200_router_topk_softmax(null, 0, 4, 8, 9, null, null, null) == 1  # k > E
-    assert lib.fma_b200_moe_gemm_forward(null, null, null, 7, 128, 2, 8, 8, null, null) == 2  # dtype
-    assert lib.fma_b200_moe_gemm_forward(null, null, null, 1, 100, 2, 8, 8, null, null) == 1  # rows_cap % 128
-    assert lib.fma_b200_moe_gemm_forward_swiglu(null, null, null, null, 0, 128, 2, 8, 8, null, null) == 2  # f32
+    assert lib.fma_b200_moe_gemm_forward(null, null, null, 7, 128, 2, 8, 8, null, 128, null) == 2  # dtype
+    assert lib.fma_b200_moe_gemm_forward(null, null, null, 1, 100, 2, 8, 8, null, 128, null) == 1  # rows_cap % 128
+    assert lib.fma_b200_moe_gemm_forward_swiglu(null, null, null, null, 0, 128, 2, 8, 8, null, 128, null) == 2  # f32
     with pytest.raises(RuntimeError, match="bad argument"):
         _native.call("fma_b200_swiglu_forward", null, 8, null, 8, null, 8, 1, 4, 12, null)  # cols % 8
     assert lib.fma_b200_moe_rows_cap(1000, 8, 128) == 2048
+    assert lib.fma_b200_moe_rows_cap(1000, 8, 256) == 3072
     assert lib.fma_b200_moe_rows_cap(0, 1, 128) == 128
     assert lib.fma_b200_continuous_count_workspace_bytes(128) == 128 + 8 * 128 * 4
 

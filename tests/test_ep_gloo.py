@@ -40,7 +40,8 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
         x = np.random.default_rng(100 + rank).standard_normal((T, H), dtype=np.float32)
         ref = O.moe_forward(x, w_gate, w_fc, w_proj, k, "f32")  # all experts, this rank's tokens
 
-        maps = O.row_maps(ref["selected"], E, 128)
+        align = moe_ep.ROW_ALIGN
+        maps = O.row_maps(ref["selected"], E, align)
         total = int(maps["pad_offsets"][-1])
         xg = np.zeros((maps["rows_cap"], H), np.float32)
         xg[maps["row_of_slot"]] = np.repeat(x, k, axis=0)
@@ -54,11 +55,11 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
         for s in range(world):
             assert recv_counts[s].tolist() == gathered[s][rank * El : (rank + 1) * El].tolist()
         send_rows, recv_rows = moe_ep.split_sizes(counts, recv_counts, world)
-        assert sum(send_rows) == total and all(r % 128 == 0 for r in send_rows + recv_rows)
+        assert sum(send_rows) == total and all(r % align == 0 for r in send_rows + recv_rows)
 
         recv = moe_ep.all_to_all_rows(torch.from_numpy(xg), send_rows, recv_rows, None).numpy()
         # receive-side maps (what fma_b200_moe_ep_recv_maps computes on the GPU)
-        seg = np.concatenate([[0], np.cumsum(-(-recv_counts.numpy().reshape(-1) // 128) * 128)])
+        seg = np.concatenate([[0], np.cumsum(-(-recv_counts.numpy().reshape(-1) // align) * align)])
         out = np.zeros((recv.shape[0], H), np.float32)
         for s in range(world):
             for e in range(El):

@@ -20,13 +20,14 @@ def _int_tensor(shape, seed, lo=-8, hi=9, dtype=torch.bfloat16):
     return torch.randint(lo, hi, shape, generator=g).to(dtype)
 
 
-def _layer_maps(counts, E):
-    """Row maps for given per-expert token counts (k = 1: slot == token)."""
+def _layer_maps(counts, E, row_align=256):
+    """Row maps for given per-expert token counts (k = 1: slot == token).  row_align 256 runs the
+    CTA-pair kernels (cta_group::2), 128 the single-CTA kernels."""
     from fma_b200.modules import _kernels as K
 
     sel = torch.cat([torch.full((c,), e, dtype=torch.int64) for e, c in enumerate(counts)])
     sel = sel[torch.randperm(sel.numel(), generator=torch.Generator().manual_seed(1))].view(-1, 1)
-    return K.moe_sort(sel.to(DEV), E), sel
+    return K.moe_sort(sel.to(DEV), E, row_align=row_align), sel
 
 
 def _segments(maps):
@@ -44,12 +45,13 @@ LAYER_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("row_align", [128, 256])
 @pytest.mark.parametrize("counts,OUT,IN", LAYER_SHAPES)
-def test_bf16_forward_dgrad_wgrad_exact(counts, OUT, IN):
+def test_bf16_forward_dgrad_wgrad_exact(counts, OUT, IN, row_align):
     from fma_b200.modules import _kernels as K
 
     E = len(counts)
-    maps, _ = _layer_maps(counts, E)
+    maps, _ = _layer_maps(counts, E, row_align)
     off, cnt = _segments(maps)
     rows = maps.rows_cap
     X = torch.zeros(rows, IN, dtype=torch.bfloat16)
@@ -60,8 +62,8 @@ def test_bf16_forward_dgrad_wgrad_exact(counts, OUT, IN):
     W = _int_tensor((E, OUT, IN), 99, -4, 5)
     Xd, dYd, Wd = X.to(DEV), dY.to(DEV), W.to(DEV)
 
-    Y = K.gemm_forward(Xd, Wd, maps.mtile_expert)
-    dX = K.gemm_dgrad(dYd, Wd, maps.mtile_expert)
+    Y = K.gemm_forward(Xd, Wd, maps.mtile_expert, row_align)
+    dX = K.gemm_dgrad(dYd, Wd, maps.mtile_expert, row_align)
     dW = K.gemm_wgrad(dYd, Xd, E, maps.pad_offsets)
     check_device_status()
     for e in range(E):
@@ -74,14 +76,15 @@ def test_bf16_forward_dgrad_wgrad_exact(counts, OUT, IN):
         assert torch.equal(dW[e].cpu(), want), f"wgrad, expert {e}"
 
 
+@pytest.mark.parametrize("row_align", [128, 256])
 @pytest.mark.parametrize("counts,I,IN", [([128, 256], 128, 64), ([5, 0, 300, 129], 256, 128), ([333, 100, 1], 200, 72)])
-def test_bf16_swiglu_epilogues(counts, I, IN):
+def test_bf16_swiglu_epilogues(counts, I, IN, row_align):
     """Fused up-projection + SwiGLU and fused dgrad + SwiGLU backward against the unfused kernels."""
     from fma_b200.modules import _kernels as K
 
     E = len(counts)
     H = IN
-    maps, _ = _layer_maps(counts, E)
+    maps, _ = _layer_maps(counts, E, row_align)
     off, cnt = _segments(maps)
     rows = maps.rows_cap
     X = torch.zeros(rows, IN, dtype=torch.bfloat16)
@@ -93,8 +96,8 @@ def test_bf16_swiglu_epilogues(counts, I, IN):
     Wproj = randn((E, H, I), torch.bfloat16, 8, 0.2)
     Xd, Wfcd, Wprojd, dOutd = X.to(DEV), Wfc.to(DEV), Wproj.to(DEV), dOut.to(DEV)
 
-    pre, act = K.gemm_forward_swiglu(Xd, Wfcd, maps.mtile_expert)
-    pre_ref = K.gemm_forward(Xd, Wfcd, maps.mtile_expert)
+    pre, act = K.gemm_forward_swiglu(Xd, Wfcd, maps.mtile_expert, row_align=row_align)
+    pre_ref = K.gemm_forward(Xd, Wfcd, maps.mtile_expert, 128)  # single-CTA kernel as the cross-check
     total = off[-1]
     assert torch.equal(pre[:total], pre_ref[:total])  # same accumulation, same rounding
     act_ref = O.swiglu_packed(to_np(pre_ref[:total]), "bf16")
@@ -102,8 +105,8 @@ def test_bf16_swiglu_epilogues(counts, I, IN):
     pad = to_np(maps.slot_of_row)[:total] < 0
     assert np.all(to_np(act[:total])[pad] == 0) and np.all(to_np(pre[:total])[pad] == 0)
 
-    d_pre = K.gemm_dgrad_swiglu(dOutd, Wprojd, pre, maps.mtile_expert)
-    d_act = K.gemm_dgrad(dOutd, Wprojd, maps.mtile_expert)
+    d_pre = K.gemm_dgrad_swiglu(dOutd, Wprojd, pre, maps.mtile_expert, row_align)
+    d_act = K.gemm_dgrad(dOutd, Wprojd, maps.mtile_expert, 128)
     gg, ug = O.swiglu_backward(to_np(pre[:total, I:]), to_np(pre[:total, :I]), to_np(d_act[:total]), "bf16")
     assert rel_l2(to_np(d_pre[:total, :I]), ug) <= 4e-3
     assert rel_l2(to_np(d_pre[:total, I:]), gg) <= 4e-3
@@ -168,7 +171,7 @@ def test_f32_forward_dgrad_wgrad(counts, OUT, IN):
         X[off[e] : off[e] + cnt[e]] = randn((cnt[e], IN), torch.float32, 10 + e)
         dY[off[e] : off[e] + cnt[e]] = randn((cnt[e], OUT), torch.float32, 50 + e)
     W = randn((E, OUT, IN), torch.float32, 99, 0.05)
-    Y = K.gemm_forward(X.to(DEV), W.to(DEV), maps.mtile_expert)
+    Y = K.gemm_forward(X.to(DEV), W.to(DEV), maps.mtile_expert)  # fp32 ignores the pairing
     dX = K.gemm_dgrad(dY.to(DEV), W.to(DEV), maps.mtile_expert)
     dW = K.gemm_wgrad(dY.to(DEV), X.to(DEV), E, maps.pad_offsets)
     for e in range(E):

@@ -41,7 +41,7 @@ def _compare_with_oracle(moe, x, g, dtype, k, tol, y, logits, dx):
     bwd = O.moe_backward(fwd, to_np(g))
     maps = moe.last_row_maps
     np.testing.assert_array_equal(to_np(maps.expert_count), fwd["expert_count"].astype(np.int64))
-    ref_maps = O.row_maps(fwd["selected"], moe.num_experts, 128)
+    ref_maps = O.row_maps(fwd["selected"], moe.num_experts, maps.row_align)
     np.testing.assert_array_equal(to_np(maps.row_of_slot), ref_maps["row_of_slot"])
     np.testing.assert_array_equal(to_np(maps.slot_of_row), ref_maps["slot_of_row"])
     errs = {

@@ -17,7 +17,7 @@ def _maps(T, E, k, seed):
 
     g = torch.Generator().manual_seed(seed)
     sel = torch.randint(0, E, (T, k), generator=g)
-    return K.moe_sort(sel.to(DEV), E), O.row_maps(sel.numpy(), E, 128)
+    return K.moe_sort(sel.to(DEV), E), O.row_maps(sel.numpy(), E, K.ROW_ALIGN)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
