@@ -74,6 +74,12 @@ __device__ __forceinline__ float sigmoid_clamped(float x) {
     return 1.0f / (1.0f + expf(-x));
 }
 
+// Same with fast intrinsics, for results that are rounded to bf16 right away (GEMM epilogues).
+__device__ __forceinline__ float sigmoid_clamped_fast(float x) {
+    x = fminf(fmaxf(x, -88.3762626647949f), 88.3762626647949f);
+    return __fdividef(1.0f, 1.0f + __expf(-x));
+}
+
 template <typename T>
 struct Elem;
 template <>

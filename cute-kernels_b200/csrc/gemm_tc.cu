@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
                         store_row32_bf16(prow + p.inter + c * 32, g, cols_left);
                     }
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped(g[i]);
+                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped_fast(g[i]);
                     if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
                 }
             } else {
@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const float d = round_bf16(da[i]);
-                            const float s = sigmoid_clamped(g[i]);
+                            const float s = sigmoid_clamped_fast(g[i]);
                             const float silu = g[i] * s;
                             da[i] = d * silu;                           // d_up
                             g[i] = d * u[i] * (s + silu * (1.f - s));   // d_gate
@@ -485,36 +485,11 @@ static int epilogue_warps() {
     return cached;
 }
 
-// Scheduler words of the dynamic tile scheduler: 64 pairs per device, handed out round-robin so that
-// launches running concurrently on different streams do not share a pair.  Zero at load; every launch
-// leaves its pair zero again.
-static __device__ unsigned int g_sched_words[64 * 2];
-
-static int next_sched_pair(unsigned int** out) {
-    static unsigned int* base[64] = {nullptr};
-    static unsigned int seq = 0;
-    int dev = -1;
-    FMAB_CUDA(cudaGetDevice(&dev));
-    FMAB_REQUIRE(dev >= 0 && dev < 64, FMA_B200_ERR_BAD_ARG, "device ordinal %d is outside [0,64)", dev);
-    if (base[dev] == nullptr) {
-        void* ptr = nullptr;
-        FMAB_CUDA(cudaGetSymbolAddress(&ptr, g_sched_words));
-        base[dev] = static_cast<unsigned int*>(ptr);
-    }
-    *out = base[dev] + 2 * (__atomic_fetch_add(&seq, 1u, __ATOMIC_RELAXED) % 64u);
-    return FMA_B200_OK;
-}
-
 template <bool A_MN, bool B_MN, int EPI, int EPI_WARPS>
 static int launch_gemm_w(const GemmParams& p_in, cudaStream_t s) {
     GemmParams p = p_in;
     if (int rc = next_sched_pair(&p.sched)) return rc;
-    static int dynamic = -1;  // FMA_B200_GEMM_STATIC_TILES=1 switches the dynamic tile scheduler off (measurement knob)
-    if (dynamic < 0) {
-        const char* env = getenv("FMA_B200_GEMM_STATIC_TILES");
-        dynamic = (env != nullptr && atoi(env) == 1) ? 0 : 1;
-    }
-    p.dynamic_tiles = dynamic;
+    p.dynamic_tiles = dynamic_tiles_enabled();
     static bool configured = false;
     auto kernel = gemm_tc_kernel<A_MN, B_MN, EPI, EPI_WARPS>;
     if (!configured) {

@@ -255,4 +255,35 @@ inline int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
 
 // Epilogue width: 8 warps (two per TMEM lane quadrant) by default; FMA_B200_GEMM_EPI_WARPS=4 selects
 
+// Scheduler words of the dynamic tile scheduler: 64 pairs per device, handed out round-robin so that
+// launches running concurrently on different streams do not share a pair.  Zero at load; every launch
+// leaves its pair zero again.
+// (one copy per translation unit that includes this header: each kernel file uses its own words)
+static __device__ unsigned int g_sched_words[64 * 2];
+
+static int next_sched_pair(unsigned int** out) {
+    static unsigned int* base[64] = {nullptr};
+    static unsigned int seq = 0;
+    int dev = -1;
+    FMAB_CUDA(cudaGetDevice(&dev));
+    FMAB_REQUIRE(dev >= 0 && dev < 64, FMA_B200_ERR_BAD_ARG, "device ordinal %d is outside [0,64)", dev);
+    if (base[dev] == nullptr) {
+        void* ptr = nullptr;
+        FMAB_CUDA(cudaGetSymbolAddress(&ptr, g_sched_words));
+        base[dev] = static_cast<unsigned int*>(ptr);
+    }
+    *out = base[dev] + 2 * (__atomic_fetch_add(&seq, 1u, __ATOMIC_RELAXED) % 64u);
+    return FMA_B200_OK;
+}
+
+// FMA_B200_GEMM_STATIC_TILES=1 switches the dynamic tile scheduler off (a measurement knob).
+static int dynamic_tiles_enabled() {
+    static int dynamic = -1;
+    if (dynamic < 0) {
+        const char* env = getenv("FMA_B200_GEMM_STATIC_TILES");
+        dynamic = (env != nullptr && atoi(env) == 1) ? 0 : 1;
+    }
+    return dynamic;
+}
+
 }  // namespace fmab

@@ -22,8 +22,11 @@
 //               stages / publishes accumulators with tcgen05.commit on both CTAs' barriers.
 //   warps 2-9   epilogue in each CTA for its own 128 rows (tensor memory lanes), as in the
 //               single-CTA kernel; they free an accumulator by arriving on the leader's barrier.
-// Tiles are assigned statically to pairs (pair p takes tiles p, p + pairs, ...), so the two CTAs
-// need no scheduling traffic.  Loads are the plain per-CTA cp.async.bulk.tensor form with the
+// Tiles are drawn from a global counter by the leader's producer thread, which publishes each tile id
+// into a small ring in BOTH CTAs' shared memory (a remote store followed by a remote mbarrier arrive);
+// every consumer of the id (the peer's producer, the MMA thread, all epilogue warps of both CTAs)
+// arrives on the leader's "slot free" barrier.  Pairs that start late or draw long tiles therefore take
+// fewer tiles (skewed expert loads, SMs shared with a collective).  Loads are the plain per-CTA cp.async.bulk.tensor form with the
 // cta_group::2 qualifier; nothing in this file broadcasts a load to several CTAs.
 // Token rows must be grouped with 256-row alignment so that both CTAs of a pair work for the same
 // expert (forward / dgrad); wgrad pairs two 128-row slabs of one expert's weight gradient.
@@ -59,6 +62,31 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Bounded wait with cluster-scope acquire, for barriers that a thread of the OTHER CTA arrives on after
+// writing ordinary shared memory of this CTA.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+    const uint64_t t0 = global_timer();
+    while (true) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if (global_timer() - t0 > 1000000000ull) {
+            *abort_flag = 1;
+            atomicExch(status, STATUS_GEMM_TIMEOUT);
+            return false;
+        }
+    }
 }
 // TMA load into this CTA's shared memory whose completion bytes are counted on the LEADER's mbarrier.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
@@ -168,6 +196,9 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
     __shared__ __align__(8) uint64_t empty_bar[PAIR_STAGES];  // each CTA waits on its own copy
     __shared__ __align__(8) uint64_t acc_full_bar[2];         // each CTA waits on its own copy
     __shared__ __align__(8) uint64_t acc_empty_bar[2];        // used in the leader only
+    __shared__ __align__(8) uint64_t sched_full_bar[SCHED_SLOTS];   // each CTA waits on its own copy
+    __shared__ __align__(8) uint64_t sched_empty_bar[SCHED_SLOTS];  // used in the leader only
+    __shared__ volatile int sched_tile[SCHED_SLOTS];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -186,6 +217,11 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&acc_full_bar[b]), 1);
             mbar_init(smem_u32(&acc_empty_bar[b]), 2 * PAIR_EPI_WARPS);  // every epilogue warp of both CTAs
+        }
+        for (int i = 0; i < SCHED_SLOTS; ++i) {
+            mbar_init(smem_u32(&sched_full_bar[i]), 1);
+            // readers of a tile id: MMA thread + peer producer + the epilogue warps of both CTAs
+            mbar_init(smem_u32(&sched_empty_bar[i]), 2 + 2 * PAIR_EPI_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -215,9 +251,40 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
-            for (int tile = pair_id; tile < total_tiles && alive; tile += n_pairs) {
+            int sslot = 0;
+            uint32_t sphase = 0;
+            int tile = pair_id;
+            while (alive) {
+                int next = -1;
+                if (leader) {
+                    // publish the tile id (or the end marker) in both CTAs, then draw the next one
+                    if (!mbar_wait_cluster(smem_u32(&sched_empty_bar[sslot]), sphase ^ 1u, abort_ptr, p.status)) {
+                        alive = false;
+                        break;
+                    }
+                    const int v = (tile < total_tiles) ? tile : -1;
+                    sched_tile[sslot] = v;
+                    st_shared_cluster_u32(map_to_rank(smem_u32(const_cast<int*>(&sched_tile[sslot])), 1), static_cast<uint32_t>(v));
+                    mbar_arrive(smem_u32(&sched_full_bar[sslot]));
+                    mbar_arrive_cluster(map_to_rank(smem_u32(&sched_full_bar[sslot]), 1));
+                    if (v >= 0)
+                        next = p.dynamic_tiles ? static_cast<int>(atomicAdd(p.sched, 1u)) + n_pairs : tile + n_pairs;
+                } else {
+                    if (!mbar_wait_cluster(smem_u32(&sched_full_bar[sslot]), sphase, abort_ptr, p.status)) {
+                        alive = false;
+                        break;
+                    }
+                    tile = sched_tile[sslot];
+                    mbar_arrive_cluster(map_to_rank(smem_u32(&sched_empty_bar[sslot]), 0));
+                    if (tile < 0) tile = total_tiles;  // end marker
+                }
+                if (++sslot == SCHED_SLOTS) {
+                    sslot = 0;
+                    sphase ^= 1u;
+                }
+                if (tile >= total_tiles) break;
                 PairTile t;
-                if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+                if (decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) {
                 for (int s = 0; s < n_seg && alive; ++s) {
                     int a_k0, b_k0, len;
                     decode_pair_segment(p, t, s, a_k0, b_k0, len);
@@ -255,6 +322,8 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         }
                     }
                 }
+                }  // valid tile
+                if (leader) tile = next;
             }
             if (!alive) {
                 for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land
@@ -268,7 +337,17 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             uint32_t phase = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
-            for (int tile = pair_id; tile < total_tiles && alive; tile += n_pairs) {
+            int sslot = 0;
+            uint32_t sphase = 0;
+            while (alive) {
+                if (!mbar_wait(smem_u32(&sched_full_bar[sslot]), sphase, abort_ptr, p.status)) break;
+                const int tile = sched_tile[sslot];
+                mbar_arrive(smem_u32(&sched_empty_bar[sslot]));
+                if (++sslot == SCHED_SLOTS) {
+                    sslot = 0;
+                    sphase ^= 1u;
+                }
+                if (tile < 0) break;
                 PairTile t;
                 if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
                 // each half of tensor memory is free once both CTAs' epilogues have drained it
@@ -339,7 +418,18 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
         const int half = (warp - 2) >> 2;
         const int row_in_tile = quad * 32 + lane;
         uint32_t acc_phase = 0;
-        for (int tile = pair_id; tile < total_tiles; tile += n_pairs) {
+        int sslot = 0;
+        uint32_t sphase = 0;
+        while (true) {
+            if (!mbar_wait_cluster(smem_u32(&sched_full_bar[sslot]), sphase, abort_ptr, p.status)) break;
+            const int tile = sched_tile[sslot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&sched_empty_bar[sslot]), 0));
+            if (++sslot == SCHED_SLOTS) {
+                sslot = 0;
+                sphase ^= 1u;
+            }
+            if (tile < 0) break;
             PairTile t;
             if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
             bool any_k = false;
@@ -398,7 +488,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         store_row32_bf16(prow + p.inter + c * 32, g, cols_left);
                     }
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped(g[i]);
+                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped_fast(g[i]);
                     if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
                 }
             } else {
@@ -433,7 +523,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const float d = round_bf16(da[i]);
-                            const float s = sigmoid_clamped(g[i]);
+                            const float s = sigmoid_clamped_fast(g[i]);
                             const float silu = g[i] * s;
                             da[i] = d * silu;
                             g[i] = d * u[i] * (s + silu * (1.f - s));
@@ -460,6 +550,15 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
+    if (threadIdx.x == 0) {
+        // the last CTA to leave puts the scheduler words back to zero for the next launch that uses them
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+            p.sched[0] = 0;
+            p.sched[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -477,7 +576,10 @@ static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s)
     FMAB_REQUIRE(total_tiles < (1LL << 31), FMA_B200_ERR_BAD_ARG, "too many tiles");
     const int64_t max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(total_tiles < max_pairs ? total_tiles : max_pairs);
-    kernel<<<2 * pairs, PAIR_THREADS, PAIR_SMEM_BYTES, s>>>(p);
+    GemmParams q = p;
+    if (int rc = next_sched_pair(&q.sched)) return rc;
+    q.dynamic_tiles = dynamic_tiles_enabled();
+    kernel<<<2 * pairs, PAIR_THREADS, PAIR_SMEM_BYTES, s>>>(q);
     return check_launch("grouped GEMM (tcgen05, CTA pairs)");
 }
 
