@@ -372,6 +372,8 @@ def main() -> None:
     ap.add_argument("--workload", default="ep_c5", choices=list(WORKLOADS) + ["count_c2"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override T (for quick runs and profiler captures)")
+    ap.add_argument("--ep-chunks", type=int, default=4, help="expert chunks whose exchanges overlap the GEMMs (N > 1)")
+    ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -407,7 +409,11 @@ def main() -> None:
     if world > 1:
         import torch.distributed as dist
 
+        os.environ.setdefault("TORCH_NCCL_HIGH_PRIORITY", "1")  # the exchanges must get SMs ahead of queued GEMMs
         dist.init_process_group("nccl", device_id=device)
+        if args.sm_reserve > 0:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            _native.call("fma_b200_set_sm_limit", sms - args.sm_reserve)
 
     def barrier():
         if world > 1:
@@ -415,6 +421,8 @@ def main() -> None:
         torch.cuda.synchronize()
 
     layer, dtype = make_layer(cfg, rank, world, device)
+    if world > 1:
+        layer.overlap_chunks = args.ep_chunks
     x, dy = make_inputs(cfg, rank, device, dtype)
     x.requires_grad_(True)
     T = cfg["T"]
@@ -550,6 +558,7 @@ def main() -> None:
         "config": {"workload": args.workload, **{k: cfg[k] for k in ("T", "H", "E", "k", "I")},
                    "tokens_per_gpu": T, "router": cfg["router"],
                    "parallelism": f"ep{world}" if world > 1 else "single",
+                   "ep_chunks": args.ep_chunks if world > 1 else None, "sm_reserve": args.sm_reserve if world > 1 else None,
                    "l2": "inputs larger than L2 (x alone is %d MB)" % (x.numel() * x.element_size() >> 20)},
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": launches,

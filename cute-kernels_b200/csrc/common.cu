@@ -21,7 +21,16 @@ int fail(int status, const char* fmt, ...) {
     return status;
 }
 
+static int g_sm_limit = 0;  // 0 = use every SM
+
+void set_sm_limit(int n) { g_sm_limit = n < 0 ? 0 : n; }
+
 int sm_count() {
+    const int all = sm_count_physical();
+    return (g_sm_limit > 0 && g_sm_limit < all) ? g_sm_limit : all;
+}
+
+int sm_count_physical() {
     static int cached[64] = {0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
@@ -64,6 +73,11 @@ const char* fma_b200_status_string(int status) {
 const char* fma_b200_last_error(void) { return fmab::last_error_buffer(); }
 
 int fma_b200_abi_version(void) { return 2; }
+
+int fma_b200_set_sm_limit(int32_t sms) {
+    fmab::set_sm_limit(sms);
+    return FMA_B200_OK;
+}
 
 int fma_b200_device_status(int32_t* status_out, void* stream) {
     FMAB_REQUIRE(status_out != nullptr, FMA_B200_ERR_BAD_ARG, "status_out is NULL");

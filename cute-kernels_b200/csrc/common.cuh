@@ -40,8 +40,11 @@ inline int check_launch(const char* what) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Number of SMs of the current device (cached per device).
+// SMs that persistent kernels may occupy: the device's SM count, or the limit set with
+// fma_b200_set_sm_limit when that is lower.
 int sm_count();
+int sm_count_physical();
+void set_sm_limit(int n);
 
 // Device status word shared by all kernels of this library (see fma_b200_device_status).
 int32_t* device_status_ptr();

@@ -26,6 +26,7 @@ SIGNATURES: dict[str, tuple] = {
     "fma_b200_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "fma_b200_last_error": (ctypes.c_char_p, []),
     "fma_b200_abi_version": (ctypes.c_int, []),
+    "fma_b200_set_sm_limit": (ctypes.c_int, [_I32]),
     "fma_b200_device_status": (ctypes.c_int, [_P, _P]),
     "fma_b200_continuous_count_workspace_bytes": (_I64, [_I32]),
     "fma_b200_continuous_count": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P, _I64, _P]),
@@ -84,7 +85,7 @@ def lib() -> ctypes.CDLL:
 
 
 # Kernels launched per entry-point call (the sort is three kernels; status queries launch none).
-KERNELS_PER_CALL = {"fma_b200_moe_sort": 3, "fma_b200_device_status": 0}
+KERNELS_PER_CALL = {"fma_b200_moe_sort": 3, "fma_b200_device_status": 0, "fma_b200_set_sm_limit": 0}
 launch_count = 0  # kernels launched through this binding since import (a plain counter for benchmarks)
 _timing: dict[str, list] | None = None  # entry point -> [(start event, end event)], when enabled
 

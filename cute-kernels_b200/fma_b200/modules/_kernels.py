@@ -129,12 +129,17 @@ def gemm_dgrad(dY: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor, ro
     return dX
 
 
-def gemm_wgrad(dY: torch.Tensor, X: torch.Tensor, E: int, seg_offsets: torch.Tensor, n_seg: int = 1) -> torch.Tensor:
+def gemm_wgrad(dY: torch.Tensor, X: torch.Tensor, E: int, seg_offsets: torch.Tensor, n_seg: int = 1,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """dW[e] = dY_e^T . X_e; `out` (contiguous [E, OUT, IN]) receives the result when given."""
     rows, OUT = dY.shape
     IN = X.size(1)
     if rows == 0:  # no rows at all (an expert-parallel rank that received nothing)
+        if out is not None:
+            return out.zero_()
         return torch.zeros(E, OUT, IN, dtype=dY.dtype, device=dY.device)
-    dW = torch.empty(E, OUT, IN, dtype=dY.dtype, device=dY.device)
+    dW = out if out is not None else torch.empty(E, OUT, IN, dtype=dY.dtype, device=dY.device)
+    assert dW.is_contiguous() and dW.shape == (E, OUT, IN)
     call("fma_b200_moe_gemm_wgrad", ptr(dY), ptr(X), ptr(dW), dtype_code(dY.dtype), rows, E, OUT, IN,
          ptr(seg_offsets), n_seg, stream_ptr(dY.device))  # fmt: skip
     return dW

@@ -5,6 +5,11 @@ The reference has no expert parallelism; this module keeps `MoE`'s interface and
 group.  Rank r owns experts [r*E/ws, (r+1)*E/ws) (`c_fc.weight [E/ws, 2I, H]`,
 `c_proj.weight [E/ws, H, I]`); the router `gate` is replicated.
 
+The local experts are processed in `overlap_chunks` chunks: the all-to-all of chunk c+1 (and the
+return exchange of chunk c-1) run on a high-priority side stream while the GEMMs of chunk c run, in the
+forward and in the backward pass.  The GEMMs draw their tiles dynamically, so they keep going on the SMs
+that the collective leaves free.
+
 Per forward, with ws ranks and El = E/ws local experts:
   1. route + stable counting sort by GLOBAL expert id: rows for rank r are contiguous, and every
      expert segment is padded to 128 rows with zero rows (same layout as the 1-GPU path);
@@ -63,57 +68,213 @@ def all_to_all_rows(rows: torch.Tensor, in_splits: list[int], out_splits: list[i
     return out
 
 
+class _ChunkPlan:
+    """Host-side description of one forward's exchanges, split into chunks of local experts so that
+    the all-to-all of one chunk runs while the GEMMs of another are busy.
+
+    Built from the two count vectors after the single device-to-host copy of the layer."""
+
+    def __init__(self, send_counts: list[int], recv_counts: list[list[int]], world_size: int, n_chunks: int):
+        E = len(send_counts)
+        El = E // world_size
+        n_chunks = max(1, min(n_chunks, El))
+        pad = lambda n: (n + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN  # noqa: E731
+        bounds = [El * c // n_chunks for c in range(n_chunks + 1)]
+        self.world_size, self.n_chunks, self.bounds = world_size, n_chunks, bounds
+        send_pad = [pad(n) for n in send_counts]
+        offs = [0]
+        for n in send_pad:
+            offs.append(offs[-1] + n)
+        self.total_send_rows = offs[-1]
+        # rows of my grouped layout that go to rank r for chunk c: [start, start + rows)
+        self.send_start = [[offs[r * El + bounds[c]] for r in range(world_size)] for c in range(n_chunks)]
+        self.send_rows = [[offs[r * El + bounds[c + 1]] - offs[r * El + bounds[c]] for r in range(world_size)]
+                          for c in range(n_chunks)]
+        # rows that source s sends me for chunk c
+        self.recv_rows = [[sum(pad(n) for n in recv_counts[s][bounds[c]:bounds[c + 1]]) for s in range(world_size)]
+                          for c in range(n_chunks)]
+
+    def experts(self, c: int) -> tuple[int, int]:
+        return self.bounds[c], self.bounds[c + 1]
+
+
+_comm_streams: dict[int, torch.cuda.Stream] = {}
+
+
+def _comm_stream(device: torch.device) -> torch.cuda.Stream:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _comm_streams:
+        _comm_streams[idx] = torch.cuda.Stream(device=device, priority=-1)
+    return _comm_streams[idx]
+
+
+def _exchange_chunk(src: torch.Tensor, src_start: list[int], src_rows: list[int], dst: torch.Tensor,
+                    dst_start: list[int], dst_rows: list[int], group) -> None:
+    """One all-to-all: rows [src_start[r], +src_rows[r]) of `src` go to rank r; rows from rank s land at
+    [dst_start[s], +dst_rows[s]) of `dst`."""
+    ins = [src[a : a + n] for a, n in zip(src_start, src_rows)]
+    outs = [dst[a : a + n] for a, n in zip(dst_start, dst_rows)]
+    dist.all_to_all(outs, ins, group=group)
+
+
+def _starts(rows: list[int]) -> list[int]:
+    out, acc = [], 0
+    for n in rows:
+        out.append(acc)
+        acc += n
+    return out
+
+
 class _EPFusedSwigluExperts(torch.autograd.Function):
+    """Expert-parallel scatter -> dispatch -> grouped GEMMs -> combine, pipelined over chunks of local
+    experts: exchanges run on a high-priority side stream and overlap the GEMMs of other chunks."""
+
     @staticmethod
-    def forward(ctx, x, weights, w_fc, w_proj, maps: K.RowMaps, group, world_size: int):
+    def forward(ctx, x, weights, w_fc, w_proj, maps: K.RowMaps, group, world_size: int, n_chunks: int):
         x = x.contiguous()
         weights = weights.contiguous()
         w_fc = w_fc.contiguous()
         w_proj = w_proj.contiguous()
-        T = x.size(0)
-        E_local = w_fc.size(0)
-        recv_counts = exchange_counts(maps.expert_count, world_size, group)
-        send_rows, recv_rows = split_sizes(maps.expert_count, recv_counts, world_size)
-        xg = K.scatter(x, maps)
-        recv = all_to_all_rows(xg, send_rows, recv_rows, group)
-        del xg
-        n_rows = recv.size(0)
+        T, H = x.shape
         dev = x.device
-        seg_offsets = torch.empty(world_size * E_local + 1, dtype=torch.int32, device=dev)
-        mtile_expert = torch.empty(max(n_rows // 128, 1), dtype=torch.int32, device=dev)
-        K.call("fma_b200_moe_ep_recv_maps", K.ptr(recv_counts), world_size, E_local, ROW_ALIGN, n_rows,
-               K.ptr(seg_offsets), K.ptr(mtile_expert), K.stream_ptr(dev))  # fmt: skip
-        pre, act = K.gemm_forward_swiglu(recv, w_fc, mtile_expert, keep_pre=True)
-        out = K.gemm_forward(act, w_proj, mtile_expert)
-        back = all_to_all_rows(out, recv_rows, send_rows, group)
-        del out
-        # `back` has pad_offsets[E] rows; the combine kernels never index beyond that
+        E_local = w_fc.size(0)
+        main = torch.cuda.current_stream(dev)
+        comm = _comm_stream(dev)
+
+        recv_counts = exchange_counts(maps.expert_count, world_size, group)
+        both = torch.cat([maps.expert_count.to(torch.int32), recv_counts.reshape(-1)]).tolist()  # the one host sync
+        E = maps.num_experts
+        plan = _ChunkPlan(both[:E], [both[E + s * E_local : E + (s + 1) * E_local] for s in range(world_size)],
+                          world_size, n_chunks)
+        C = plan.n_chunks
+
+        xg = K.scatter(x, maps)
+        ready = torch.cuda.Event()
+        ready.record(main)
+
+        recv, seg_offs, mtiles, pres, acts = [], [], [], [], []
+        back = torch.empty(plan.total_send_rows, H, dtype=x.dtype, device=dev)
+        back.record_stream(comm)
+        xg.record_stream(comm)
+        dispatched = [torch.cuda.Event() for _ in range(C)]
+        combined = torch.cuda.Event()
+
+        def dispatch(c: int) -> None:
+            with torch.cuda.stream(comm):
+                buf = torch.empty(sum(plan.recv_rows[c]), H, dtype=x.dtype, device=dev)
+                buf.record_stream(main)
+                _exchange_chunk(xg, plan.send_start[c], plan.send_rows[c], buf, _starts(plan.recv_rows[c]),
+                                plan.recv_rows[c], group)
+                dispatched[c].record(comm)
+            recv.append(buf)
+
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+        dispatch(0)
+        if C > 1:
+            dispatch(1)
+        for c in range(C):
+            e0, e1 = plan.experts(c)
+            n_rows = recv[c].size(0)
+            counts_c = recv_counts[:, e0:e1].contiguous()
+            seg = torch.empty(world_size * (e1 - e0) + 1, dtype=torch.int32, device=dev)
+            mt = torch.empty(max(n_rows // 128, 1), dtype=torch.int32, device=dev)
+            K.call("fma_b200_moe_ep_recv_maps", K.ptr(counts_c), world_size, e1 - e0, ROW_ALIGN, n_rows, K.ptr(seg),
+                   K.ptr(mt), K.stream_ptr(dev))  # fmt: skip
+            main.wait_event(dispatched[c])
+            pre, act = K.gemm_forward_swiglu(recv[c], w_fc[e0:e1], mt, keep_pre=True)
+            out = K.gemm_forward(act, w_proj[e0:e1], mt)
+            done = torch.cuda.Event()
+            done.record(main)
+            out.record_stream(comm)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                _exchange_chunk(out, _starts(plan.recv_rows[c]), plan.recv_rows[c], back, plan.send_start[c],
+                                plan.send_rows[c], group)
+                if c == C - 1:
+                    combined.record(comm)
+            if c + 2 < C:
+                dispatch(c + 2)
+            seg_offs.append(seg)
+            mtiles.append(mt)
+            pres.append(pre)
+            acts.append(act)
+        main.wait_event(combined)
         y = K.combine(back, weights, maps, T)
-        ctx.save_for_backward(recv, pre, act, back, weights, w_fc, w_proj, seg_offsets, mtile_expert)
-        ctx.maps, ctx.group, ctx.world_size, ctx.T = maps, group, world_size, T
-        ctx.send_rows, ctx.recv_rows = send_rows, recv_rows
+
+        ctx.save_for_backward(back, weights, w_fc, w_proj, *recv, *pres, *acts, *seg_offs, *mtiles)
+        ctx.maps, ctx.group, ctx.world_size, ctx.T, ctx.plan = maps, group, world_size, T, plan
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        recv, pre, act, back, weights, w_fc, w_proj, seg_offsets, mtile_expert = ctx.saved_tensors
+        plan: _ChunkPlan = ctx.plan
+        C = plan.n_chunks
+        saved = ctx.saved_tensors
+        back, weights, w_fc, w_proj = saved[:4]
+        recv, pres, acts, seg_offs, mtiles = (saved[4 + i * C : 4 + (i + 1) * C] for i in range(5))
         maps, group, ws = ctx.maps, ctx.group, ctx.world_size
-        E_local = w_fc.size(0)
+        dev = dy.device
+        H = dy.size(1)
+        main = torch.cuda.current_stream(dev)
+        comm = _comm_stream(dev)
         need_x, need_w, need_fc, need_proj = ctx.needs_input_grad[:4]
+
         d_back, d_w = K.combine_backward(dy.contiguous(), back, weights, maps, need_w)
-        d_out = all_to_all_rows(d_back, ctx.send_rows, ctx.recv_rows, group)
-        del d_back
-        d_w_proj = K.gemm_wgrad(d_out, act, E_local, seg_offsets, n_seg=ws) if need_proj else None
-        d_x = d_w_fc = None
-        if need_x or need_fc:
-            d_pre = K.gemm_dgrad_swiglu(d_out, w_proj, pre, mtile_expert)
-            if need_fc:
-                d_w_fc = K.gemm_wgrad(d_pre, recv, E_local, seg_offsets, n_seg=ws)
-            if need_x:
-                d_recv = K.gemm_dgrad(d_pre, w_fc, mtile_expert)
-                d_xg = all_to_all_rows(d_recv, ctx.recv_rows, ctx.send_rows, group)
-                d_x = K.scatter_backward(d_xg, maps, ctx.T)
-        return d_x, d_w, d_w_fc, d_w_proj, None, None, None
+        ready = torch.cuda.Event()
+        ready.record(main)
+        d_back.record_stream(comm)
+        d_w_fc = torch.empty_like(w_fc) if need_fc else None
+        d_w_proj = torch.empty_like(w_proj) if need_proj else None
+        d_xg = torch.empty(plan.total_send_rows, H, dtype=dy.dtype, device=dev) if need_x else None
+        if d_xg is not None:
+            d_xg.record_stream(comm)
+        d_outs: list[torch.Tensor] = []
+        dispatched = [torch.cuda.Event() for _ in range(C)]
+        returned = torch.cuda.Event()
+
+        def dispatch(c: int) -> None:
+            with torch.cuda.stream(comm):
+                buf = torch.empty(sum(plan.recv_rows[c]), H, dtype=dy.dtype, device=dev)
+                buf.record_stream(main)
+                _exchange_chunk(d_back, plan.send_start[c], plan.send_rows[c], buf, _starts(plan.recv_rows[c]),
+                                plan.recv_rows[c], group)
+                dispatched[c].record(comm)
+            d_outs.append(buf)
+
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+        dispatch(0)
+        if C > 1:
+            dispatch(1)
+        for c in range(C):
+            e0, e1 = plan.experts(c)
+            main.wait_event(dispatched[c])
+            d_out = d_outs[c]
+            if need_proj:
+                K.gemm_wgrad(d_out, acts[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_proj[e0:e1])
+            if need_x or need_fc:
+                d_pre = K.gemm_dgrad_swiglu(d_out, w_proj[e0:e1], pres[c], mtiles[c])
+                if need_fc:
+                    K.gemm_wgrad(d_pre, recv[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_fc[e0:e1])
+                if need_x:
+                    d_recv = K.gemm_dgrad(d_pre, w_fc[e0:e1], mtiles[c])
+                    done = torch.cuda.Event()
+                    done.record(main)
+                    d_recv.record_stream(comm)
+                    with torch.cuda.stream(comm):
+                        comm.wait_event(done)
+                        _exchange_chunk(d_recv, _starts(plan.recv_rows[c]), plan.recv_rows[c], d_xg,
+                                        plan.send_start[c], plan.send_rows[c], group)
+                        if c == C - 1:
+                            returned.record(comm)
+            if c + 2 < C:
+                dispatch(c + 2)
+        d_x = None
+        if need_x:
+            main.wait_event(returned)
+            d_x = K.scatter_backward(d_xg, maps, ctx.T)
+        return d_x, d_w, d_w_fc, d_w_proj, None, None, None, None
 
 
 class ExpertParallelMoE(MoE):
@@ -131,8 +292,10 @@ class ExpertParallelMoE(MoE):
         add_bias: bool,
         std: float,
         process_group=None,
+        overlap_chunks: int = 4,
     ) -> None:
         self.process_group = process_group
+        self.overlap_chunks = overlap_chunks
         self.ep_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.ep_rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         if num_experts % self.ep_size != 0:
@@ -157,7 +320,7 @@ class ExpertParallelMoE(MoE):
             maps = K.moe_sort(selected_experts, self.num_experts)
         self.last_row_maps = maps
         return _EPFusedSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
-                                           self.process_group, self.ep_size)  # fmt: skip
+                                           self.process_group, self.ep_size, self.overlap_chunks)  # fmt: skip
 
 
 def shard_expert_state_dict(full: dict, rank: int, world_size: int) -> dict:

@@ -41,6 +41,14 @@ const char* fma_b200_last_error(void);
 int fma_b200_abi_version(void);
 
 /*
+ * Upper bound on the SMs that the persistent kernels of this library occupy (grid size of the grouped
+ * GEMMs); 0 restores "all SMs".  Process-wide.  The expert-parallel layer lowers it while NCCL
+ * all-to-all kernels run next to the GEMMs so that the collective always finds free SMs.
+ * No reference counterpart.
+ */
+int fma_b200_set_sm_limit(int32_t sms);
+
+/*
  * Device status word.  Kernels that wait on barriers (the tensor-core grouped GEMM)
  * bound every wait; a wait that runs out records a non-zero code here and the
  * kernel returns after releasing what it holds.  This call copies the word of the
