@@ -372,7 +372,7 @@ def main() -> None:
     ap.add_argument("--workload", default="ep_c5", choices=list(WORKLOADS) + ["count_c2"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override T (for quick runs and profiler captures)")
-    ap.add_argument("--ep-chunks", type=int, default=4, help="expert chunks whose exchanges overlap the GEMMs (N > 1)")
+    ap.add_argument("--ep-chunks", type=int, default=6, help="expert chunks whose exchanges overlap the GEMMs (N > 1)")
     ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

@@ -75,6 +75,7 @@ struct GemmParams {
     int32_t n_seg;                // wgrad: segments per expert
     int32_t inter;                // SwiGLU: intermediate size I
     int32_t dynamic_tiles;        // 1: tiles drawn from the global counter; 0: tile = blockIdx.x + i * gridDim.x
+    int32_t pair_skew;            // CTA-pair kernel: k-blocks by which accumulator half 1 trails half 0
 };
 
 // ---------------------------------------------------------------------------

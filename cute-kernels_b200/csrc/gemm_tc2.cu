@@ -350,40 +350,65 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 if (tile < 0) break;
                 PairTile t;
                 if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
-                // each half of tensor memory is free once both CTAs' epilogues have drained it
-                bool waited[PAIR_HALVES] = {false, false};
-                uint32_t accumulate = 0;
-                for (int s = 0; s < n_seg && alive; ++s) {
+                // k-blocks of the tile (all segments); only their count matters to this warp
+                int nkb = 0;
+                for (int s = 0; s < n_seg; ++s) {
                     int a_k0, b_k0, len;
                     decode_pair_segment(p, t, s, a_k0, b_k0, len);
-                    for (int k = 0; k < len; k += BK) {
+                    nkb += (len + BK - 1) / BK;
+                }
+                // Half 1 runs `skew` k-blocks behind half 0: at the end of a tile half 0 is published (and its
+                // epilogue starts) while half 1 still has MMAs to run, and at the start of the next tile half
+                // 0 can run while half 1 is still being stored.  A ring stage is released after BOTH halves
+                // have read it, i.e. `skew` k-blocks later than without the skew.
+                const int skew = (t.halves == 2) ? min(p.pair_skew, nkb) : 0;
+                for (int step = 0; step < nkb + skew && alive; ++step) {
+                    if (step < nkb) {  // half 0 on k-block `step`, which is the ring's current stage
                         if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_ptr, p.status)) {
                             alive = false;
                             break;
                         }
                         tc_fence_after();
+                        if (step == 0) {
+                            if (!mbar_wait(smem_u32(&acc_empty_bar[0]), acc_phase ^ 1u, abort_ptr, p.status)) {
+                                alive = false;
+                                break;
+                            }
+                            tc_fence_after();
+                        }
                         const uint32_t sa = ring + stage * PAIR_STAGE_BYTES;
-                        const uint32_t sb = sa + A_STAGE_BYTES;
                         const uint64_t a_desc = make_smem_desc<A_MN>(sa);
-                        for (int h = 0; h < t.halves && alive; ++h) {
-                            if (!waited[h]) {
-                                if (!mbar_wait(smem_u32(&acc_empty_bar[h]), acc_phase ^ 1u, abort_ptr, p.status)) {
+                        const uint64_t b_desc = make_smem_desc<B_MN>(sa + A_STAGE_BYTES);
+#pragma unroll
+                        for (int ks = 0; ks < BK / UMMA_K; ++ks)
+                            tc_mma_pair(tmem_base, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
+                                        b_desc + ((ks * desc_k_step<B_MN>()) >> 4), idesc, (step | ks) ? 1u : 0u);
+                        if (step == nkb - 1) tc_commit_pair(smem_u32(&acc_full_bar[0]));
+                    }
+                    const int kb1 = step - skew;  // k-block of half 1 in this step
+                    if (kb1 >= 0) {
+                        // its stage is `skew` positions behind the ring's head (fewer once half 0 has finished)
+                        const int behind = (step < nkb) ? skew : (nkb - kb1);  // the head already points past the last k-block
+                        const int st1 = (stage + PAIR_STAGES - behind) % PAIR_STAGES;
+                        if (t.halves == 2) {
+                            if (kb1 == 0) {
+                                if (!mbar_wait(smem_u32(&acc_empty_bar[1]), acc_phase ^ 1u, abort_ptr, p.status)) {
                                     alive = false;
                                     break;
                                 }
                                 tc_fence_after();
-                                waited[h] = true;
                             }
-                            const uint64_t b_desc = make_smem_desc<B_MN>(sb + h * PAIR_B_BYTES);
-                            const uint32_t d_tmem = tmem_base + h * BN;
+                            const uint32_t sa = ring + st1 * PAIR_STAGE_BYTES;
+                            const uint64_t a_desc = make_smem_desc<A_MN>(sa);
+                            const uint64_t b_desc = make_smem_desc<B_MN>(sa + A_STAGE_BYTES + PAIR_B_BYTES);
 #pragma unroll
                             for (int ks = 0; ks < BK / UMMA_K; ++ks)
-                                tc_mma_pair(d_tmem, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
-                                            b_desc + ((ks * desc_k_step<B_MN>()) >> 4), idesc, (accumulate | ks) ? 1u : 0u);
+                                tc_mma_pair(tmem_base + BN, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
+                                            b_desc + ((ks * desc_k_step<B_MN>()) >> 4), idesc, (kb1 | ks) ? 1u : 0u);
                         }
-                        if (!alive) break;
-                        accumulate = 1;
-                        tc_commit_pair(smem_u32(&empty_bar[stage]));  // frees the stage in both CTAs
+                        tc_commit_pair(smem_u32(&empty_bar[st1]));  // both halves are done with this stage
+                    }
+                    if (step < nkb) {
                         if (++stage == PAIR_STAGES) {
                             stage = 0;
                             phase ^= 1u;
@@ -391,10 +416,10 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     }
                 }
                 if (!alive) break;
-                for (int h = 0; h < t.halves; ++h) {
-                    if (accumulate) {
-                        tc_commit_pair(smem_u32(&acc_full_bar[h]));
-                    } else {  // empty reduction: both epilogues write zeros
+                if (nkb > 0) {
+                    if (t.halves == 2) tc_commit_pair(smem_u32(&acc_full_bar[1]));
+                } else {  // empty reduction: both epilogues write zeros
+                    for (int h = 0; h < t.halves && alive; ++h) {
                         if (!mbar_wait(smem_u32(&acc_empty_bar[h]), acc_phase ^ 1u, abort_ptr, p.status)) {
                             alive = false;
                             break;
@@ -402,6 +427,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         mbar_arrive(smem_u32(&acc_full_bar[h]));
                         mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[h]), 1));
                     }
+                    if (!alive) break;
                 }
                 if (t.halves == 1) {
                     // keep half 1's barriers in step with the tile count: pass its phase through unused
@@ -564,6 +590,17 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
+// k-blocks by which accumulator half 1 trails half 0 (0..2); FMA_B200_GEMM_SKEW overrides the default.
+static int pair_skew() {
+    static int v = -1;
+    if (v < 0) {
+        const char* env = getenv("FMA_B200_GEMM_SKEW");
+        v = env ? atoi(env) : 1;  // 1 measured best with a 4-stage ring (2 starves the ring)
+        if (v < 0 || v > 2) v = 1;
+    }
+    return v;
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s) {
     static bool configured = false;
@@ -579,6 +616,7 @@ static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s)
     GemmParams q = p;
     if (int rc = next_sched_pair(&q.sched)) return rc;
     q.dynamic_tiles = dynamic_tiles_enabled();
+    q.pair_skew = pair_skew();
     kernel<<<2 * pairs, PAIR_THREADS, PAIR_SMEM_BYTES, s>>>(q);
     return check_launch("grouped GEMM (tcgen05, CTA pairs)");
 }

@@ -68,6 +68,21 @@ def all_to_all_rows(rows: torch.Tensor, in_splits: list[int], out_splits: list[i
     return out
 
 
+def chunk_bounds(n_local_experts: int, n_chunks: int) -> list[int]:
+    """Expert boundaries of the pipeline chunks.  The first dispatch and the last return exchange cannot
+    hide behind any GEMM, so with 4 or more chunks the first and last chunk are made small (about 1/16
+    of the experts each) and the middle ones share the rest evenly."""
+    El = n_local_experts
+    n_chunks = max(1, min(n_chunks, El))
+    if n_chunks < 4 or El < 8:
+        return [El * c // n_chunks for c in range(n_chunks + 1)]
+    edge = max(1, El // 16)
+    inner = n_chunks - 2
+    rest = El - 2 * edge
+    bounds = [0] + [edge + rest * c // inner for c in range(inner + 1)] + [El]
+    return sorted(set(bounds))
+
+
 class _ChunkPlan:
     """Host-side description of one forward's exchanges, split into chunks of local experts so that
     the all-to-all of one chunk runs while the GEMMs of another are busy.
@@ -77,9 +92,9 @@ class _ChunkPlan:
     def __init__(self, send_counts: list[int], recv_counts: list[list[int]], world_size: int, n_chunks: int):
         E = len(send_counts)
         El = E // world_size
-        n_chunks = max(1, min(n_chunks, El))
         pad = lambda n: (n + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN  # noqa: E731
-        bounds = [El * c // n_chunks for c in range(n_chunks + 1)]
+        bounds = chunk_bounds(El, n_chunks)
+        n_chunks = len(bounds) - 1
         self.world_size, self.n_chunks, self.bounds = world_size, n_chunks, bounds
         send_pad = [pad(n) for n in send_counts]
         offs = [0]
@@ -292,7 +307,7 @@ class ExpertParallelMoE(MoE):
         add_bias: bool,
         std: float,
         process_group=None,
-        overlap_chunks: int = 4,
+        overlap_chunks: int = 6,
     ) -> None:
         self.process_group = process_group
         self.overlap_chunks = overlap_chunks
