@@ -6,21 +6,7 @@ import torch
 
 from .. import _native
 from ..kernel_backend import KernelBackend
-
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
-
-
-def _workspace(device: torch.device, size: int) -> torch.Tensor:
-    """Per-device scratch for the block partials; its ticket word starts at zero and every call
-    leaves it at zero, so it is allocated once and reused by later calls on the same stream order."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), size)
-    ws = _workspaces.get(key)
-    if ws is None:
-        nbytes = _native.lib().fma_b200_continuous_count_workspace_bytes(size)
-        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
-
+from ._custom_ops import continuous_count_op
 
 @torch.no_grad()
 def continuous_count(
@@ -37,16 +23,7 @@ def continuous_count(
     assert x.dim() == 1, "x should be 1-dimensional"
     assert x.dtype in [torch.int32, torch.long]
     _native.require_cuda(x)
-    x = x.contiguous()
-    if x.data_ptr() % 16 != 0:  # the kernel reads 128-bit vectors
-        x = x.clone()
 
     output = torch.empty(size, dtype=torch.uint32, device=x.device)
-    ws = _workspace(x.device, size)
-    args = (_native.ptr(x), x.element_size(), x.numel(), size, _native.ptr(output), _native.ptr(ws), ws.numel())
-    with torch.cuda.device(x.device):
-        if _variant is None:  # the library picks the shared-memory scheme from `size`
-            _native.call("fma_b200_continuous_count", *args, _native.stream_ptr(x.device))
-        else:  # measurement hook: force one scheme
-            _native.call("fma_b200_continuous_count_variant", *args, _variant, _native.stream_ptr(x.device))
+    continuous_count_op(x, output, size, -1 if _variant is None else _variant)
     return output

@@ -6,18 +6,12 @@ import torch
 
 from .. import _native
 from ..kernel_backend import KernelBackend
-
-
-def _rows_cols(t: torch.Tensor) -> tuple[int, int]:
-    cols = t.size(-1)
-    return (t.numel() // cols if cols else 0), cols
-
-
-def _pitch(t: torch.Tensor) -> int:
-    """Row pitch in elements of a tensor viewed as [rows, cols]; the tensor must be row-regular."""
-    if t.dim() == 1:
-        return t.size(0)
-    return t.stride(-2)
+from ._custom_ops import (
+    swiglu_backward_op,
+    swiglu_forward_op,
+    swiglu_packed_backward_op,
+    swiglu_packed_forward_op,
+)
 
 
 def _as_rows(t: torch.Tensor) -> torch.Tensor:
@@ -41,24 +35,11 @@ def _as_rows(t: torch.Tensor) -> torch.Tensor:
 
 
 def _forward(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor) -> None:
-    rows, cols = _rows_cols(out)
-    with torch.cuda.device(out.device):
-        _native.call(
-            "fma_b200_swiglu_forward",
-            _native.ptr(gate), _pitch(gate), _native.ptr(up), _pitch(up), _native.ptr(out), _pitch(out),
-            _native.dtype_code(out.dtype), rows, cols, _native.stream_ptr(out.device),
-        )  # fmt: skip
+    swiglu_forward_op(gate, up, out)
 
 
 def _backward(gate, up, dy, gate_grad, up_grad) -> None:
-    rows, cols = _rows_cols(dy)
-    with torch.cuda.device(dy.device):
-        _native.call(
-            "fma_b200_swiglu_backward",
-            _native.ptr(gate), _pitch(gate), _native.ptr(up), _pitch(up), _native.ptr(dy), _pitch(dy),
-            _native.ptr(gate_grad), _pitch(gate_grad), _native.ptr(up_grad), _pitch(up_grad),
-            _native.dtype_code(dy.dtype), rows, cols, _native.stream_ptr(dy.device),
-        )  # fmt: skip
+    swiglu_backward_op(gate, up, dy, gate_grad, up_grad)
 
 
 class _Swiglu(torch.autograd.Function):
@@ -88,10 +69,9 @@ class _SwigluPacked(torch.autograd.Function):
     def forward(ctx, x: torch.Tensor) -> torch.Tensor:
         _native.require_cuda(x)
         assert x.size(-1) % 2 == 0
-        x = x.contiguous()
-        up, gate = x.chunk(2, dim=-1)  # first half is `up`, second half is `gate`
+        x = x.contiguous()  # first half of the last dimension is `up`, second half is `gate`
         out = torch.empty(*x.shape[:-1], x.size(-1) // 2, dtype=x.dtype, device=x.device)
-        _forward(gate, up, out)
+        swiglu_packed_forward_op(x, out)
         ctx.save_for_backward(x)
         return out
 
@@ -100,9 +80,7 @@ class _SwigluPacked(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         output_grad = output_grad.contiguous()
         x_grad = torch.empty_like(x)
-        up, gate = x.chunk(2, dim=-1)
-        up_grad, gate_grad = x_grad.chunk(2, dim=-1)
-        _backward(gate, up, output_grad, gate_grad, up_grad)
+        swiglu_packed_backward_op(x, output_grad, x_grad)
         return x_grad
 
 

@@ -1,0 +1,60 @@
+"""The op surface under torch.compile(fullgraph=True), as the reference tests every op
+(tests/ops/continuous_count_test.py:25, swiglu_test.py, grouped_gemm_test.py:25): the kernels are
+registered as torch.library custom ops, so the compiler traces through the wrappers."""
+
+import pytest
+import torch
+
+from _util import DEV, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def test_continuous_count_compiled():
+    import fma_b200
+
+    fn = torch.compile(fma_b200.continuous_count, fullgraph=True)
+    ids = torch.randint(0, 72, (16393,), generator=torch.Generator().manual_seed(1))
+    for dtype in (torch.int32, torch.int64):
+        got = fn(ids.to(dtype).to(DEV), 72)
+        assert got.dtype == torch.uint32
+        assert torch.equal(got.to(torch.int64).cpu(), torch.bincount(ids, minlength=72))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_compiled_forward_backward(dtype):
+    import fma_b200
+
+    gate = randn((257, 264), dtype, 1, 3.0).to(DEV).requires_grad_(True)
+    up = randn((257, 264), dtype, 2).to(DEV).requires_grad_(True)
+    dy = randn((257, 264), dtype, 3).to(DEV)
+    y = fma_b200.swiglu(gate, up)
+    y.backward(dy)
+    want = (y.detach().clone(), gate.grad.clone(), up.grad.clone())
+    gate.grad = up.grad = None
+    yc = torch.compile(fma_b200.swiglu, fullgraph=True)(gate, up)
+    yc.backward(dy)
+    assert torch.equal(yc, want[0]) and torch.equal(gate.grad, want[1]) and torch.equal(up.grad, want[2])
+
+    x = torch.cat([up.detach(), gate.detach()], -1).requires_grad_(True)
+    yp = torch.compile(fma_b200.swiglu_packed, fullgraph=True)(x)
+    yp.backward(dy)
+    assert torch.equal(yp, want[0])
+    assert torch.equal(x.grad, torch.cat([want[2], want[1]], -1))
+
+
+def test_grouped_gemm_compiled():
+    import fma_b200
+
+    Ms, N, Kd = [256, 72, 0, 136], 264, 192
+    g = torch.Generator().manual_seed(3)
+    As = [torch.randint(-8, 9, (m, Kd), generator=g).to(torch.bfloat16) for m in Ms]
+    Bs = [torch.randint(-8, 9, (N, Kd), generator=g).to(torch.bfloat16) for _ in Ms]
+    A = torch.cat([a.reshape(-1) for a in As]).to(DEV)
+    B = torch.cat([b.reshape(-1) for b in Bs]).to(DEV)
+    u32 = lambda v: torch.tensor(v, dtype=torch.uint32, device=DEV)  # noqa: E731
+    fn = torch.compile(fma_b200.grouped_gemm, fullgraph=True)
+    out = fn(A=A, B=B, C=None, M_array=u32(Ms), N_array=u32([N] * 4), K_array=u32([Kd] * 4),
+             output_shape=(sum(Ms) * N,), is_A_transposed=False, is_B_transposed=True)
+    want = torch.cat([(a.float() @ b.float().T).to(torch.bfloat16).reshape(-1) for a, b in zip(As, Bs)])
+    assert torch.equal(out.cpu(), want)
