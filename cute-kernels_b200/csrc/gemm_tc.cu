@@ -10,7 +10,9 @@
 //               thread; warps 2-5 take the first half of the tile's columns, warps 6-9 the second),
 //               optional SwiGLU forward / backward math, bf16 rounding, 128-bit stores.
 // Tensor memory holds two 128x256 fp32 accumulators (all 512 columns), so the epilogue of tile
-// i overlaps the main loop of tile i+1.
+// i overlaps the main loop of tile i+1.  Tiles are drawn from a global counter by the producer thread
+// and published to the other warps through a small shared-memory ring, so CTAs that start late or
+// draw long tiles take fewer of them.
 //
 // Operands may be K-major (the reduction index is contiguous in memory) or MN-major (the row /
 // column index is contiguous); the latter is what dgrad (B = W[e], [K,N] row-major) and wgrad
