@@ -176,6 +176,61 @@ combine_backward_kernel(const T* __restrict__ dy, const T* __restrict__ expert_o
     }
 }
 
+// grouped[p, :] += bias[e(p), :] on token rows (padding rows stay zero); one warp per grouped row.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+bias_add_kernel(T* __restrict__ grouped, const T* __restrict__ bias, int64_t rows_cap, int C,
+                const int32_t* __restrict__ mtile_expert, const int32_t* __restrict__ slot_of_row) {
+    constexpr int V = Elem<T>::kPerVec;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowWarps + warp;
+    if (row >= rows_cap) return;
+    const int e = mtile_expert[row >> 7];
+    if (e < 0 || slot_of_row[row] < 0) return;
+    uint4* dst = reinterpret_cast<uint4*>(grouped + row * C);
+    const uint4* b = reinterpret_cast<const uint4*>(bias + static_cast<int64_t>(e) * C);
+    for (int c = lane; c < C / V; c += 32) {
+        float x[V], y[V];
+        Elem<T>::unpack(dst[c], x);
+        Elem<T>::unpack(ld_global_16(b + c), y);
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[i] += y[i];
+        dst[c] = Elem<T>::pack(x);
+    }
+}
+
+// d_bias[e, c] = sum over the rows of expert e of d_grouped[row, c] (padding rows are zero), fp32
+// accumulation in row order: deterministic.  Block = (expert, 256 columns), thread = one column.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_grad_kernel(const T* __restrict__ d_grouped, int C, const int32_t* __restrict__ pad_offsets,
+                 T* __restrict__ d_bias) {
+    const int e = blockIdx.y;
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= C) return;
+    const int64_t beg = pad_offsets[e], end = pad_offsets[e + 1];
+    float acc = 0.f;
+    int64_t r = beg;
+    for (; r + 4 <= end; r += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const T x = d_grouped[(r + u) * C + c];
+            if constexpr (sizeof(T) == 2) v[u] = __bfloat162float(x); else v[u] = x;
+        }
+        acc += v[0];
+        acc += v[1];
+        acc += v[2];
+        acc += v[3];
+    }
+    for (; r < end; ++r) {
+        const T x = d_grouped[r * C + c];
+        if constexpr (sizeof(T) == 2) acc += __bfloat162float(x); else acc += x;
+    }
+    if constexpr (sizeof(T) == 2) d_bias[static_cast<int64_t>(e) * C + c] = __float2bfloat16_rn(acc);
+    else d_bias[static_cast<int64_t>(e) * C + c] = acc;
+}
+
 static int check_rows_args(int32_t dtype, int64_t T, int32_t H, int32_t k) {
     FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
     FMAB_REQUIRE(T >= 0 && T < (1LL << 31), FMA_B200_ERR_BAD_ARG, "T=%lld", (long long)T);
@@ -275,6 +330,45 @@ int fma_b200_moe_combine_backward(const void* dy, const void* expert_out, const 
             static_cast<const __nv_bfloat16*>(weights), T, H, k, row_of_slot, slot_of_row, pad_offsets, E, tok_blocks,
             static_cast<__nv_bfloat16*>(d_expert_out), static_cast<__nv_bfloat16*>(d_weights));
     return check_launch("moe_combine_backward");
+}
+
+int fma_b200_moe_bias_add(void* grouped, const void* bias, int32_t dtype, int64_t rows_cap, int32_t C,
+                          const int32_t* mtile_expert, const int32_t* slot_of_row, void* stream) {
+    using namespace fmab;
+    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    const int per_vec = (dtype == FMA_B200_F32) ? 4 : 8;
+    FMAB_REQUIRE(C >= per_vec && C % per_vec == 0, FMA_B200_ERR_BAD_ARG, "C=%d is not a multiple of 16 bytes", C);
+    FMAB_REQUIRE(rows_cap >= 0 && rows_cap % 128 == 0, FMA_B200_ERR_BAD_ARG, "rows_cap=%lld", (long long)rows_cap);
+    if (rows_cap == 0) return FMA_B200_OK;
+    FMAB_REQUIRE(grouped && bias && mtile_expert && slot_of_row, FMA_B200_ERR_BAD_ARG, "NULL pointer");
+    FMAB_REQUIRE(aligned16(grouped) && aligned16(bias), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = static_cast<unsigned>((rows_cap + kRowWarps - 1) / kRowWarps);
+    if (dtype == FMA_B200_F32)
+        bias_add_kernel<float><<<grid, kRowThreads, 0, s>>>(static_cast<float*>(grouped), static_cast<const float*>(bias),
+                                                           rows_cap, C, mtile_expert, slot_of_row);
+    else
+        bias_add_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(static_cast<__nv_bfloat16*>(grouped),
+                                                                   static_cast<const __nv_bfloat16*>(bias), rows_cap, C,
+                                                                   mtile_expert, slot_of_row);
+    return check_launch("moe_bias_add");
+}
+
+int fma_b200_moe_bias_grad(const void* d_grouped, int32_t dtype, int32_t E, int32_t C, const int32_t* pad_offsets,
+                           void* d_bias, void* stream) {
+    using namespace fmab;
+    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    FMAB_REQUIRE(E >= 1 && E <= 65535 && C >= 1, FMA_B200_ERR_BAD_ARG, "E=%d C=%d", E, C);
+    FMAB_REQUIRE(d_grouped && pad_offsets && d_bias, FMA_B200_ERR_BAD_ARG, "NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid((C + 255) / 256, E);
+    if (dtype == FMA_B200_F32)
+        bias_grad_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(d_grouped), C, pad_offsets,
+                                                    static_cast<float*>(d_bias));
+    else
+        bias_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(d_grouped), C,
+                                                            pad_offsets, static_cast<__nv_bfloat16*>(d_bias));
+    return check_launch("moe_bias_grad");
 }
 
 }  // extern "C"

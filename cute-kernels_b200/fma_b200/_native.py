@@ -45,6 +45,8 @@ SIGNATURES: dict[str, tuple] = {
         ctypes.c_int,
         [_P, _P, _P, _I32, _I64, _I32, _I32, _P, _P, _P, _I32, _I64, _P, _P, _P],
     ),
+    "fma_b200_moe_bias_add": (ctypes.c_int, [_P, _P, _I32, _I64, _I32, _P, _P, _P]),
+    "fma_b200_moe_bias_grad": (ctypes.c_int, [_P, _I32, _I32, _I32, _P, _P, _P]),
     "fma_b200_swiglu_forward": (ctypes.c_int, [_P, _I64, _P, _I64, _P, _I64, _I32, _I64, _I64, _P]),
     "fma_b200_swiglu_backward": (
         ctypes.c_int,

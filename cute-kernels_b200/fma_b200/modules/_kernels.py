@@ -183,3 +183,19 @@ def gemm_dgrad_swiglu(d_out: torch.Tensor, W: torch.Tensor, pre: torch.Tensor, m
     call("fma_b200_swiglu_backward", ptr(gate), 2 * I, ptr(up), 2 * I, ptr(d_act), I, ptr(d_gate), 2 * I, ptr(d_up),
          2 * I, dtype_code(d_out.dtype), rows, I, stream_ptr(dev))  # fmt: skip
     return d_pre
+
+
+def bias_add_(grouped: torch.Tensor, bias: torch.Tensor, maps: RowMaps) -> torch.Tensor:
+    """In place: grouped[p] += bias[expert(p)] on token rows (padding rows stay zero)."""
+    rows, C = grouped.shape
+    call("fma_b200_moe_bias_add", ptr(grouped), ptr(bias), dtype_code(grouped.dtype), rows, C, ptr(maps.mtile_expert),
+         ptr(maps.slot_of_row), stream_ptr(grouped.device))  # fmt: skip
+    return grouped
+
+
+def bias_grad(d_grouped: torch.Tensor, maps: RowMaps) -> torch.Tensor:
+    C = d_grouped.size(1)
+    d_bias = torch.empty(maps.num_experts, C, dtype=d_grouped.dtype, device=d_grouped.device)
+    call("fma_b200_moe_bias_grad", ptr(d_grouped), dtype_code(d_grouped.dtype), maps.num_experts, C,
+         ptr(maps.pad_offsets), ptr(d_bias), stream_ptr(d_grouped.device))  # fmt: skip
+    return d_bias

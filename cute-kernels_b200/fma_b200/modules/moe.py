@@ -60,12 +60,15 @@ class _ExpertLinear(torch.autograd.Function):
     """Y[p] = X[p] . W[e(p)]^T over the grouped layout (Experts.cuda_forward of the reference)."""
 
     @staticmethod
-    def forward(ctx, x, weight, maps: K.RowMaps):
+    def forward(ctx, x, weight, bias, maps: K.RowMaps):
         x = x.contiguous()
         weight = weight.contiguous()
         ctx.save_for_backward(x, weight)
         ctx.maps = maps
-        return K.gemm_forward(x, weight, maps.mtile_expert, maps.row_align)
+        y = K.gemm_forward(x, weight, maps.mtile_expert, maps.row_align)
+        if bias is not None:
+            K.bias_add_(y, bias.contiguous(), maps)
+        return y
 
     @staticmethod
     def backward(ctx, d_y):
@@ -74,7 +77,8 @@ class _ExpertLinear(torch.autograd.Function):
         d_y = d_y.contiguous()
         d_x = K.gemm_dgrad(d_y, weight, maps.mtile_expert, maps.row_align) if ctx.needs_input_grad[0] else None
         d_w = K.gemm_wgrad(d_y, x, weight.size(0), maps.pad_offsets) if ctx.needs_input_grad[1] else None
-        return d_x, d_w, None
+        d_b = K.bias_grad(d_y, maps) if ctx.needs_input_grad[2] else None
+        return d_x, d_w, d_b, None
 
 
 class _Combine(torch.autograd.Function):
@@ -168,9 +172,7 @@ class Experts(nn.Module):
 
     def grouped_forward(self, input: torch.Tensor, maps: K.RowMaps) -> torch.Tensor:
         """Y = X . W[e]^T over the grouped layout (rows of expert e in maps.pad_offsets[e:e+2])."""
-        if self.bias is not None:
-            raise NotImplementedError("Experts with add_bias=True are not supported by the B200 kernels yet")
-        return _ExpertLinear.apply(input, self.weight, maps)
+        return _ExpertLinear.apply(input, self.weight, self.bias, maps)
 
     def extra_repr(self):
         return "num_experts={}, in_features={}, out_features={}".format(

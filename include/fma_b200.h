@@ -219,6 +219,17 @@ int fma_b200_moe_combine_backward(const void* dy, const void* expert_out, const 
                                   const int32_t* slot_of_row, const int32_t* pad_offsets, int32_t E,
                                   int64_t rows_cap, void* d_expert_out, void* d_weights, void* stream);
 
+/*
+ * Per-expert bias of `Experts` (add_bias=True): grouped[p,:] += bias[e(p),:] on token rows, padding rows
+ * stay zero; and its gradient d_bias[e,:] = sum of d_grouped over the rows of expert e (fp32 sum in row
+ * order).  Replaces the bias of F.linear in Experts.torch_forward (fma/modules/moe/__init__.py:102-105);
+ * the reference's CUDA path drops the bias (:89-92).  C = bias width, a multiple of 16 bytes.
+ */
+int fma_b200_moe_bias_add(void* grouped, const void* bias, int32_t dtype, int64_t rows_cap, int32_t C,
+                          const int32_t* mtile_expert, const int32_t* slot_of_row, void* stream);
+int fma_b200_moe_bias_grad(const void* d_grouped, int32_t dtype, int32_t E, int32_t C, const int32_t* pad_offsets,
+                           void* d_bias, void* stream);
+
 /* ======================================================================= */
 /* swiglu                                                                   */
 /* ======================================================================= */

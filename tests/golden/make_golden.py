@@ -34,7 +34,7 @@ def f32(t: torch.Tensor) -> np.ndarray:
     return t.detach().float().contiguous().numpy()
 
 
-def build_reference_moe(fma, E, k, H, I, dtype, seed):
+def build_reference_moe(fma, E, k, H, I, dtype, seed, add_bias=False):
     from fma import KernelBackend
     import fma.modules.moe as ref_moe
 
@@ -45,16 +45,19 @@ def build_reference_moe(fma, E, k, H, I, dtype, seed):
         x, kernel_backend_forward=KernelBackend.torch, kernel_backend_backward=KernelBackend.torch
     )
     torch.manual_seed(seed)
-    moe = ref_moe.MoE(E, k, H, I, act, True, False, 0.02)
+    moe = ref_moe.MoE(E, k, H, I, act, True, add_bias, 0.02)
     with torch.no_grad():
         moe.gate.weight.normal_(0, 0.02)
+        if add_bias:  # the reference initialises biases to zero; random ones make the fixture meaningful
+            moe.c_fc.bias.normal_(0, 0.5)
+            moe.c_proj.bias.normal_(0, 0.5)
     return moe.to(dtype)
 
 
-def run_layer(fma, T, H, E, k, I, dtype, seed):
+def run_layer(fma, T, H, E, k, I, dtype, seed, add_bias=False):
     from fma import KernelBackend
 
-    moe = build_reference_moe(fma, E, k, H, I, dtype, seed)
+    moe = build_reference_moe(fma, E, k, H, I, dtype, seed, add_bias)
     x = torch.randn(T, H).to(dtype).requires_grad_(True)
     g = torch.randn(T, H).to(dtype)
     y, logits = moe(x, kernel_backend=KernelBackend.torch)
@@ -64,7 +67,12 @@ def run_layer(fma, T, H, E, k, I, dtype, seed):
         ref_sorted_e, ref_sorted_s = sel.flatten().sort()
         st_sorted_e, st_sorted_s = sel.flatten().sort(stable=True)
         count = fma.continuous_count(ref_sorted_e, E, kernel_backend=KernelBackend.torch)
+    extra = {}
+    if add_bias:
+        extra = {"b_fc": f32(moe.c_fc.bias), "b_proj": f32(moe.c_proj.bias), "d_b_fc": f32(moe.c_fc.bias.grad),
+                 "d_b_proj": f32(moe.c_proj.bias.grad)}  # fmt: skip
     return {
+        **extra,
         "x": f32(x), "g": f32(g), "w_gate": f32(moe.gate.weight), "w_fc": f32(moe.c_fc.weight),
         "w_proj": f32(moe.c_proj.weight), "y": f32(y), "router_logits": f32(logits), "dx": f32(x.grad),
         "d_w_gate": f32(moe.gate.weight.grad), "d_w_fc": f32(moe.c_fc.weight.grad),
@@ -78,6 +86,7 @@ def run_layer(fma, T, H, E, k, I, dtype, seed):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only-bias", action="store_true", help="write only the add_bias=True layer fixtures")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -85,6 +94,19 @@ def main() -> None:
     from fma import KernelBackend
 
     torch.set_num_threads(8)
+
+    # ---- layer with per-expert biases (add_bias=True) ------------------------------------------
+    biased = {
+        "layer_f32_bias": dict(T=80, H=64, E=5, k=2, I=48, dtype=torch.float32, seed=15, add_bias=True),
+        "layer_bf16_bias": dict(T=128, H=64, E=8, k=2, I=64, dtype=torch.bfloat16, seed=16, add_bias=True),
+    }
+    for name, cfg in biased.items():
+        out, _ = run_layer(fma, **cfg)
+        meta = {k: (str(v) if isinstance(v, torch.dtype) else v) for k, v in cfg.items()}
+        np.savez_compressed(HERE / f"{name}.npz", meta=json.dumps(meta), **out)
+        print(name, {k: v.shape for k, v in out.items() if k in ("y", "dx", "d_b_fc")})
+    if args.only_bias:
+        return
 
     # ---- layer, small shapes, every tensor stored --------------------------------------------
     small = {

@@ -80,6 +80,40 @@ def test_golden_cases(golden_dir, name):
         np.testing.assert_array_equal(to_np(moe.last_row_maps.expert_count), z["expert_count"])
 
 
+@pytest.mark.parametrize("name", ["layer_f32_bias", "layer_bf16_bias"])
+def test_golden_cases_with_expert_bias(golden_dir, name):
+    """add_bias=True: per-expert bias kernels (forward add on token rows, column-sum gradient)."""
+    import fma_b200
+
+    z = np.load(golden_dir / f"{name}.npz")
+    meta = json.loads(str(z["meta"]))
+    dtype = torch.bfloat16 if "bfloat16" in meta["dtype"] else torch.float32
+    E, k, H, I = meta["E"], meta["k"], meta["H"], meta["I"]
+    moe = fma_b200.MoE(E, k, H, I, fma_b200.swiglu_packed, True, True, 0.02)
+    with torch.no_grad():
+        for p, key in ((moe.gate.weight, "w_gate"), (moe.c_fc.weight, "w_fc"), (moe.c_proj.weight, "w_proj"),
+                       (moe.c_fc.bias, "b_fc"), (moe.c_proj.bias, "b_proj")):  # fmt: skip
+            p.copy_(torch.from_numpy(z[key]))
+    moe = moe.to(DEV).to(dtype)
+    x = torch.from_numpy(z["x"]).to(dtype)
+    g = torch.from_numpy(z["g"]).to(dtype)
+    y, logits, dx = _run(moe, x, g)
+    od = ORACLE_DTYPE[dtype]
+    fwd = O.moe_forward(to_np(x), z["w_gate"], z["w_fc"], z["w_proj"], k, od, logits=to_np(logits),
+                        b_fc=z["b_fc"], b_proj=z["b_proj"])  # fmt: skip
+    bwd = O.moe_backward(fwd, to_np(g))
+    tol = TOL[dtype]
+    got = {"y": y, "dx": dx, "d_w_fc": moe.c_fc.weight.grad, "d_w_proj": moe.c_proj.weight.grad,
+           "d_b_fc": moe.c_fc.bias.grad, "d_b_proj": moe.c_proj.bias.grad}  # fmt: skip
+    want = {"y": fwd["y"], **{n: bwd[n] for n in got if n != "y"}}
+    errs = {n: rel_l2(to_np(got[n]), want[n]) for n in got}
+    assert all(e <= tol for e in errs.values()), errs
+    if np.array_equal(fwd["selected"], z["selected"]):
+        direct_tol = 2e-5 if dtype == torch.float32 else 1e-2
+        for n in got:
+            assert rel_l2(to_np(got[n]), z[n]) <= direct_tol, n
+
+
 def test_config1_fp32_full_size(golden_dir):
     """T=4096, H=1024, E=8, top-2, I=512, fp32, seed 0: the small configuration at full size."""
     torch.manual_seed(0)

@@ -69,3 +69,31 @@ def test_combine_and_backward(dtype, T, H, E, k):
     # deterministic: same bits on a second run
     y2 = K.combine(out.to(DEV), w.to(DEV), maps, T)
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,E,k", CASES)
+def test_expert_bias_add_and_grad(dtype, T, H, E, k):
+    """grouped[p] += bias[e(p)] on token rows only (padding rows stay exactly zero), and the
+    per-expert column sums that are the bias gradient."""
+    from fma_b200.modules import _kernels as K
+
+    maps, ref = _maps(T, E, k, seed=T + 3 * H)
+    x = randn((T, H), dtype, seed=4)
+    bias = randn((E, H), dtype, seed=5)
+    grouped = K.scatter(x.to(DEV), maps)
+    before = to_np(grouped).copy()
+    K.bias_add_(grouped, bias.to(DEV), maps)
+    total = int(ref["pad_offsets"][-1])
+    slot = ref["slot_of_row"][:total]
+    expert_of_row = np.repeat(np.arange(E), np.diff(ref["pad_offsets"]))
+    want = before[:total].copy()
+    valid = slot >= 0
+    summed = (torch.from_numpy(before[:total][valid]) + torch.from_numpy(to_np(bias)[expert_of_row[valid]])).to(dtype)
+    want[valid] = summed.float().numpy()
+    np.testing.assert_array_equal(to_np(grouped)[:total], want)  # one rounded add per element: exact
+
+    d = to_np(grouped).astype(np.float64)
+    got = K.bias_grad(grouped, maps)
+    want_g = np.stack([d[ref["pad_offsets"][e] : ref["pad_offsets"][e + 1]].sum(0) for e in range(E)])
+    assert rel_l2(to_np(got), want_g) <= (1e-5 if dtype == torch.float32 else 4e-3)

@@ -57,6 +57,21 @@ def test_layer_matches_reference(golden_dir, name):
         assert np.abs(z["d_w_gate"]).max() == 0 and np.abs(bwd["d_w_gate"]).max() == 0
 
 
+@pytest.mark.parametrize("name", ["layer_f32_bias", "layer_bf16_bias"])
+def test_layer_with_expert_bias_matches_reference(golden_dir, name):
+    z, meta = _load(golden_dir, name)
+    dtype = "bf16" if "bfloat16" in meta["dtype"] else "f32"
+    fwd = O.moe_forward(z["x"], z["w_gate"], z["w_fc"], z["w_proj"], meta["k"], dtype, logits=z["router_logits"],
+                        b_fc=z["b_fc"], b_proj=z["b_proj"])
+    assert np.array_equal(np.sort(fwd["selected"], -1), np.sort(z["selected"], -1))
+    np.testing.assert_array_equal(fwd["expert_count"], z["expert_count"])
+    bwd = O.moe_backward(fwd, z["g"])
+    tol = 2e-6 if dtype == "f32" else 6e-3
+    assert O.rel_l2(fwd["y"], z["y"]) < tol
+    for key in ("dx", "d_w_fc", "d_w_proj", "d_b_fc", "d_b_proj"):
+        assert O.rel_l2(bwd[key], z[key]) < tol, key
+
+
 def test_layer_config1_statistics(golden_dir):
     """The small fp32 configuration (T=4096, H=1024, E=8, top-2, I=512, seed 0) regenerated from its
     recipe and compared with the statistics the reference produced."""
