@@ -373,6 +373,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override T (for quick runs and profiler captures)")
     ap.add_argument("--ep-chunks", type=int, default=6, help="expert chunks whose exchanges overlap the GEMMs (N > 1)")
+    ap.add_argument("--ep-transport", choices=["auto", "peer", "nccl"], default="auto",
+                    help="row exchange of the expert-parallel layer: copy-engine pushes into peer-mapped arenas, "
+                         "or NCCL all-to-all; auto = peer when the arenas can be mapped (N > 1)")
     ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -423,6 +426,7 @@ def main() -> None:
     layer, dtype = make_layer(cfg, rank, world, device)
     if world > 1:
         layer.overlap_chunks = args.ep_chunks
+        layer.transport = args.ep_transport
     x, dy = make_inputs(cfg, rank, device, dtype)
     x.requires_grad_(True)
     T = cfg["T"]
@@ -559,7 +563,8 @@ def main() -> None:
         "config": {"workload": args.workload, **{k: cfg[k] for k in ("T", "H", "E", "k", "I")},
                    "tokens_per_gpu": T, "router": cfg["router"],
                    "parallelism": f"ep{world}" if world > 1 else "single",
-                   "ep_chunks": args.ep_chunks if world > 1 else None, "sm_reserve": args.sm_reserve if world > 1 else None,
+                   "ep_chunks": args.ep_chunks if world > 1 else None,
+                   "ep_transport": layer.last_transport if world > 1 else None, "sm_reserve": args.sm_reserve if world > 1 else None,
                    "l2": "inputs larger than L2 (x alone is %d MB)" % (x.numel() * x.element_size() >> 20)},
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": launches,

@@ -47,6 +47,13 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "fma_b200_moe_bias_add": (ctypes.c_int, [_P, _P, _I32, _I64, _I32, _P, _P, _P]),
     "fma_b200_moe_bias_grad": (ctypes.c_int, [_P, _I32, _I32, _I32, _P, _P, _P]),
+    "fma_b200_peer_buffer_create": (ctypes.c_int, [_I64, _P, _P]),
+    "fma_b200_peer_buffer_open": (ctypes.c_int, [_P, _P]),
+    "fma_b200_peer_buffer_close": (ctypes.c_int, [_P]),
+    "fma_b200_peer_buffer_destroy": (ctypes.c_int, [_P]),
+    "fma_b200_peer_copy": (ctypes.c_int, [_I32, _P, _P, _P, _P]),
+    "fma_b200_peer_signal": (ctypes.c_int, [_I32, _P, _I32, _P]),
+    "fma_b200_peer_wait": (ctypes.c_int, [_P, _I32, _I32, _I32, _P]),
     "fma_b200_swiglu_forward": (ctypes.c_int, [_P, _I64, _P, _I64, _P, _I64, _I32, _I64, _I64, _P]),
     "fma_b200_swiglu_backward": (
         ctypes.c_int,
@@ -87,7 +94,11 @@ def lib() -> ctypes.CDLL:
 
 
 # Kernels launched per entry-point call (the sort is three kernels; status queries launch none).
-KERNELS_PER_CALL = {"fma_b200_moe_sort": 3, "fma_b200_device_status": 0, "fma_b200_set_sm_limit": 0}
+KERNELS_PER_CALL = {
+    "fma_b200_moe_sort": 3, "fma_b200_device_status": 0, "fma_b200_set_sm_limit": 0, "fma_b200_peer_buffer_create": 0,
+    "fma_b200_peer_buffer_open": 0, "fma_b200_peer_buffer_close": 0, "fma_b200_peer_buffer_destroy": 0,
+    "fma_b200_peer_copy": 0,
+}  # fmt: skip
 launch_count = 0  # kernels launched through this binding since import (a plain counter for benchmarks)
 _timing: dict[str, list] | None = None  # entry point -> [(start event, end event)], when enabled
 

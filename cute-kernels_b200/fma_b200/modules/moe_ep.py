@@ -308,9 +308,18 @@ class ExpertParallelMoE(MoE):
         std: float,
         process_group=None,
         overlap_chunks: int = 6,
+        transport: str = "auto",
+        capacity_factor: float = 1.5,
     ) -> None:
+        if transport not in ("auto", "peer", "nccl"):
+            raise ValueError(f"transport={transport!r}: expected 'auto', 'peer' or 'nccl'")
         self.process_group = process_group
         self.overlap_chunks = overlap_chunks
+        self.transport = transport
+        self.capacity_factor = capacity_factor
+        self.last_transport = None  # "peer" or "nccl": what the most recent forward used
+        self._arena = None
+        self._peer_unavailable = None  # reason text once the peer transport has been given up
         self.ep_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.ep_rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         if num_experts % self.ep_size != 0:
@@ -334,8 +343,59 @@ class ExpertParallelMoE(MoE):
         with torch.no_grad():
             maps = K.moe_sort(selected_experts, self.num_experts)
         self.last_row_maps = maps
+        if self.transport != "nccl" and self._peer_unavailable is None:
+            y = self._compute_experts_peer(hidden_states, router_weights, maps)
+            if y is not None:
+                self.last_transport = "peer"
+                return y
+        self.last_transport = "nccl"
         return _EPFusedSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
                                            self.process_group, self.ep_size, self.overlap_chunks)  # fmt: skip
+
+
+    def _compute_experts_peer(self, hidden_states, router_weights, maps):
+        """The layer over the peer-memory transport, or None when this call has to use NCCL: the arenas
+        cannot be set up (transport="auto"), the previous forward's arena contents are still needed by a
+        backward that has not run, or a rank would receive more rows than its arena holds.  Every rank
+        takes the same decision, from the same gathered numbers."""
+        from . import moe_ep_peer as P
+
+        dev = hidden_states.device
+        E, ws = self.num_experts, self.ep_size
+        info = torch.cat([maps.expert_count.to(torch.int32),
+                          torch.full((1,), maps.rows_cap, dtype=torch.int32, device=dev)])  # fmt: skip
+        gathered = torch.empty(ws, E + 1, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(gathered, info, group=self.process_group)
+        table = gathered.tolist()  # the one host synchronisation of the layer
+        counts = [row[:E] for row in table]
+        need = max(row[E] for row in table)
+        arena = self._arena
+        H, dtype = hidden_states.size(1), hidden_states.dtype
+        if arena is None or arena.send_cap < need or arena.hidden != H or arena.dtype != dtype:
+            if arena is not None and arena.busy:
+                return None
+            if arena is not None:
+                arena.close()
+                self._arena = None
+            recv_cap = (int(self.capacity_factor * need) + 127) // 128 * 128
+            try:
+                arena = self._arena = P.PeerArena(self.process_group, dev, need, max(recv_cap, need), H, dtype)
+            except P.PeerTransportUnavailable as e:
+                if self.transport == "peer":
+                    raise
+                self._peer_unavailable = str(e)
+                return None
+        plan = P.PeerPlan(counts, self.ep_rank, self.overlap_chunks)
+        if arena.busy or max(plan.total_recv_rows) > arena.recv_cap:
+            return None
+        return P._EPPeerSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
+                                            arena, plan, gathered[:, :E].contiguous())  # fmt: skip
+
+    def close_peer_transport(self) -> None:
+        """Collective: frees the peer-memory arena (the next forward would create a new one)."""
+        if self._arena is not None:
+            self._arena.close()
+            self._arena = None
 
 
 def shard_expert_state_dict(full: dict, rank: int, world_size: int) -> dict:

@@ -1,0 +1,371 @@
+"""Peer-memory transport of the expert-parallel MoE (one node, NVLink / NVSwitch).
+
+Instead of NCCL all-to-all kernels, which take SMs from the grouped GEMMs they overlap with, every
+rank owns an arena that all ranks of the node map (CUDA IPC) and rows travel as copy-engine pushes
+straight into the receiver's arena:
+
+    sender, side stream:   copies (my padded segments -> the slot the receiver's layout reserves for
+                           them), then one flag per receiver = sequence number of this layer call
+    receiver, main stream: a small kernel waits (bounded) for the flags of the chunk, then the grouped
+                           GEMMs read the rows in place: the arena region IS the GEMM operand.
+
+Each rank knows every rank's per-expert row counts (one all-gather of E+1 integers per forward, which
+is also the only host synchronisation and the cross-rank barrier that makes arena reuse safe), so
+source and destination offsets of every block are computed on the host by `PeerPlan`, identically on
+all ranks.
+
+Arena regions (rows of H elements):
+    recv     rows dispatched to my experts, [chunk][source rank][local expert] padded segments
+    d_out    the same layout for the gradient rows dispatched in the backward pass
+    back     expert outputs returned to me, in my own grouped layout (operand of the weighted combine)
+    d_xg     gradient rows returned to me in the backward pass, same layout
+"""
+
+from __future__ import annotations
+
+import ctypes
+import weakref
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from . import _kernels as K
+from .moe_ep import ROW_ALIGN, _comm_stream, chunk_bounds
+
+MAX_CHUNKS = 16
+MAX_RANKS = 64
+REGIONS = ("recv", "d_out", "back", "d_xg")
+FLAG_FWD_DISPATCH, FLAG_FWD_RETURN, FLAG_BWD_DISPATCH, FLAG_BWD_RETURN = range(4)
+FLAG_BYTES = 4 * 4 * MAX_CHUNKS * MAX_RANKS
+WAIT_TIMEOUT_MS = 4000
+
+
+class PeerTransportUnavailable(RuntimeError):
+    """Raised on every rank of the group when the arenas could not be created or mapped."""
+
+
+def _pad(n: int, align: int = ROW_ALIGN) -> int:
+    return (n + align - 1) // align * align
+
+
+def _prefix(values: list[int]) -> list[int]:
+    out = [0]
+    for v in values:
+        out.append(out[-1] + v)
+    return out
+
+
+class PeerPlan:
+    """Where every block of rows goes, from the matrix counts[s][e] = rows that rank s routes to
+    (global) expert e.  Pure host arithmetic, the same on every rank.
+
+    A block is the run of padded expert segments that one source sends to one destination for one
+    chunk of the destination's local experts.  Copies are (peer, dst_row, src_row, n_rows)."""
+
+    def __init__(self, counts: list[list[int]], rank: int, n_chunks: int, row_align: int = ROW_ALIGN):
+        ws, E = len(counts), len(counts[0])
+        if E % ws:
+            raise ValueError(f"{E} experts over {ws} ranks")
+        El = E // ws
+        self.world_size, self.rank, self.num_local_experts = ws, rank, El
+        self.bounds = chunk_bounds(El, min(n_chunks, MAX_CHUNKS))
+        C = self.n_chunks = len(self.bounds) - 1
+        self.counts = counts
+        # S[s][e]: first row of expert e in rank s's own grouped layout
+        self.S = [_prefix([_pad(n, row_align) for n in row]) for row in counts]
+        b = self.bounds
+        # rows[s][r][c]: size of the block s -> r, chunk c
+        self.rows = [[[self.S[s][r * El + b[c + 1]] - self.S[s][r * El + b[c]] for c in range(C)] for r in range(ws)]
+                     for s in range(ws)]  # fmt: skip
+        # receive layout of rank r: chunk after chunk, inside a chunk source after source
+        self.recv_base = [_prefix([sum(self.rows[s][r][c] for s in range(ws)) for c in range(C)]) for r in range(ws)]
+        self.src_off = [[_prefix([self.rows[s][r][c] for s in range(ws)]) for c in range(C)] for r in range(ws)]
+        self.total_recv_rows = [self.recv_base[r][C] for r in range(ws)]
+        self.total_send_rows = self.S[rank][E]
+
+    def experts(self, c: int) -> tuple[int, int]:
+        return self.bounds[c], self.bounds[c + 1]
+
+    def peer_order(self) -> list[int]:
+        """Peers starting after this rank, this rank last: at any time the senders aim at different
+        receivers."""
+        return [(self.rank + 1 + i) % self.world_size for i in range(self.world_size)]
+
+    def recv_chunk(self, c: int) -> tuple[int, int]:
+        """(first row, rows) of chunk c in this rank's receive regions."""
+        base = self.recv_base[self.rank]
+        return base[c], base[c + 1] - base[c]
+
+    def dispatch_copies(self, c: int) -> list[tuple[int, int, int, int]]:
+        """My grouped layout -> the receive region of every rank."""
+        me, El, b = self.rank, self.num_local_experts, self.bounds
+        return [(r, self.recv_base[r][c] + self.src_off[r][c][me], self.S[me][r * El + b[c]], self.rows[me][r][c])
+                for r in self.peer_order()]  # fmt: skip
+
+    def return_copies(self, c: int) -> list[tuple[int, int, int, int]]:
+        """Rows of my chunk-local result (receive order) -> the grouped layout of the rank they came from."""
+        me, El, b = self.rank, self.num_local_experts, self.bounds
+        return [(s, self.S[s][me * El + b[c]], self.src_off[me][c][s], self.rows[s][me][c]) for s in self.peer_order()]
+
+
+class _RawCudaMemory:
+    """Exposes a raw device allocation through __cuda_array_interface__ so that torch can view it."""
+
+    def __init__(self, address: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
+
+
+class PeerArena:
+    """One rank's arena plus the mappings of every other rank's arena.  Creation is collective."""
+
+    def __init__(self, group, device: torch.device, send_cap: int, recv_cap: int, hidden: int, dtype: torch.dtype):
+        self.group, self.device = group, device
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world_size > MAX_RANKS:
+            raise RuntimeError(f"peer transport supports up to {MAX_RANKS} ranks")
+        self.send_cap, self.recv_cap, self.hidden, self.dtype = send_cap, recv_cap, hidden, dtype
+        self.row_bytes = hidden * torch.empty((), dtype=dtype).element_size()
+        caps = {"recv": recv_cap, "d_out": recv_cap, "back": send_cap, "d_xg": send_cap}
+        self.region_off, off = {}, FLAG_BYTES
+        for name in REGIONS:
+            self.region_off[name] = off
+            off += _pad(caps[name] * self.row_bytes, 256)
+        self.nbytes = off
+        self.seq = 0
+        self._lease = None
+
+        self.local_ptr, self.peer_ptrs = 0, []
+        local = ctypes.c_void_p()
+        handle = (ctypes.c_uint8 * 64)()
+        with torch.cuda.device(device):
+            # every phase ends in a collective that all ranks reach, whether their part worked or not
+            error = None
+            try:
+                _native.call("fma_b200_peer_buffer_create", self.nbytes, ctypes.byref(local), handle)
+                self.local_ptr = int(local.value)
+            except RuntimeError as e:
+                error = str(e)
+            created = [None] * self.world_size
+            dist.all_gather_object(created, (error, bytes(handle)), group=group)
+            opened: list[int] = []
+            if error is None and all(err is None for err, _ in created):
+                try:
+                    for r, (_, h) in enumerate(created):
+                        if r == self.rank:
+                            opened.append(self.local_ptr)
+                            continue
+                        p = ctypes.c_void_p()
+                        _native.call("fma_b200_peer_buffer_open", (ctypes.c_uint8 * 64).from_buffer_copy(h),
+                                     ctypes.byref(p))  # fmt: skip
+                        opened.append(int(p.value))
+                except RuntimeError as e:
+                    error = str(e)
+            else:
+                error = error or "another rank could not allocate its arena"
+            errors = [None] * self.world_size
+            dist.all_gather_object(errors, error, group=group)
+            if any(e is not None for e in errors):
+                for r, p in enumerate(opened):
+                    if r != self.rank:
+                        _native.lib().fma_b200_peer_buffer_close(ctypes.c_void_p(p))
+                dist.barrier(group)
+                if self.local_ptr:
+                    _native.lib().fma_b200_peer_buffer_destroy(ctypes.c_void_p(self.local_ptr))
+                    self.local_ptr = 0
+                raise PeerTransportUnavailable("; ".join(f"rank {r}: {e}" for r, e in enumerate(errors) if e))
+            self.peer_ptrs = opened
+        raw = torch.as_tensor(_RawCudaMemory(self.local_ptr, self.nbytes), device=device)
+        self.flags = raw[:FLAG_BYTES].view(torch.int32)
+        self.regions = {
+            name: raw[self.region_off[name] : self.region_off[name] + caps[name] * self.row_bytes].view(dtype).view(
+                caps[name], hidden)
+            for name in REGIONS
+        }  # fmt: skip
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    # ---- lifetime ---------------------------------------------------------------------------
+    def lease(self):
+        """Token held by the autograd node of a forward whose regions the backward still needs."""
+
+        class _Lease:
+            pass
+
+        token = _Lease()
+        self._lease = weakref.ref(token)
+        return token
+
+    @property
+    def busy(self) -> bool:
+        return self._lease is not None and self._lease() is not None
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' arenas and frees this rank's."""
+        if self.local_ptr == 0:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        with torch.cuda.device(self.device):
+            for r, p in enumerate(self.peer_ptrs):
+                if r != self.rank:
+                    _native.call("fma_b200_peer_buffer_close", ctypes.c_void_p(p))
+            dist.barrier(self.group)
+            self.flags, self.regions = None, {}
+            _native.call("fma_b200_peer_buffer_destroy", ctypes.c_void_p(self.local_ptr))
+        self.local_ptr, self.peer_ptrs = 0, []
+
+    # ---- transport (all on the current stream) ------------------------------------------------
+    @staticmethod
+    def _flag_index(kind: int, chunk: int, src: int) -> int:
+        return (kind * MAX_CHUNKS + chunk) * MAX_RANKS + src
+
+    def push(self, copies: list[tuple[int, int, int, int]], src: torch.Tensor, region: str) -> None:
+        """copies = (peer, dst_row, src_row, n_rows): rows of `src` into `region` of each peer's arena."""
+        copies = [c for c in copies if c[3] > 0]
+        n = len(copies)
+        if n == 0:
+            return
+        rb, base, off = self.row_bytes, src.data_ptr(), self.region_off[region]
+        dst = (ctypes.c_uint64 * n)(*[self.peer_ptrs[r] + off + d * rb for r, d, _, _ in copies])
+        srcs = (ctypes.c_uint64 * n)(*[base + s * rb for _, _, s, _ in copies])
+        nbytes = (ctypes.c_int64 * n)(*[k * rb for _, _, _, k in copies])
+        _native.call("fma_b200_peer_copy", n, dst, srcs, nbytes, _native.stream_ptr(self.device))
+
+    def signal(self, kind: int, chunk: int, seq: int) -> None:
+        n = self.world_size
+        idx = 4 * self._flag_index(kind, chunk, self.rank)
+        addrs = (ctypes.c_uint64 * n)(*[p + idx for p in self.peer_ptrs])
+        _native.call("fma_b200_peer_signal", n, addrs, seq, _native.stream_ptr(self.device))
+
+    def wait(self, kind: int, chunk: int, seq: int) -> None:
+        first = self._flag_index(kind, chunk, 0)
+        _native.call("fma_b200_peer_wait", ctypes.c_void_p(self.flags.data_ptr() + 4 * first), self.world_size, seq,
+                     WAIT_TIMEOUT_MS, _native.stream_ptr(self.device))  # fmt: skip
+
+
+class _EPPeerSwigluExperts(torch.autograd.Function):
+    """scatter -> push to the expert ranks -> grouped GEMMs on the arena -> push back -> combine,
+    pipelined over chunks of local experts; the backward mirrors it."""
+
+    @staticmethod
+    def forward(ctx, x, weights, w_fc, w_proj, maps: K.RowMaps, arena: PeerArena, plan: PeerPlan, counts_dev):
+        x, weights, w_fc, w_proj = x.contiguous(), weights.contiguous(), w_fc.contiguous(), w_proj.contiguous()
+        T = x.size(0)
+        dev = x.device
+        me, ws, El, C = plan.rank, plan.world_size, plan.num_local_experts, plan.n_chunks
+        main, comm = torch.cuda.current_stream(dev), _comm_stream(dev)
+        arena.seq += 1
+        seq = arena.seq
+
+        xg = K.scatter(x, maps)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        xg.record_stream(comm)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+
+        def dispatch(c: int) -> None:
+            with torch.cuda.stream(comm):
+                arena.push(plan.dispatch_copies(c), xg, "recv")
+                arena.signal(FLAG_FWD_DISPATCH, c, seq)
+
+        dispatch(0)
+        if C > 1:
+            dispatch(1)
+        recv, seg_offs, mtiles, pres, acts = [], [], [], [], []
+        for c in range(C):
+            e0, e1 = plan.experts(c)
+            base, n_rows = plan.recv_chunk(c)
+            rows = arena.regions["recv"][base : base + n_rows]
+            counts_c = counts_dev[:, me * El + e0 : me * El + e1].contiguous()
+            seg = torch.empty(ws * (e1 - e0) + 1, dtype=torch.int32, device=dev)
+            mt = torch.empty(max(n_rows // 128, 1), dtype=torch.int32, device=dev)
+            K.call("fma_b200_moe_ep_recv_maps", K.ptr(counts_c), ws, e1 - e0, ROW_ALIGN, n_rows, K.ptr(seg), K.ptr(mt),
+                   K.stream_ptr(dev))  # fmt: skip
+            arena.wait(FLAG_FWD_DISPATCH, c, seq)
+            pre, act = K.gemm_forward_swiglu(rows, w_fc[e0:e1], mt, keep_pre=True)
+            out = K.gemm_forward(act, w_proj[e0:e1], mt)
+            done = torch.cuda.Event()
+            done.record(main)
+            out.record_stream(comm)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                arena.push(plan.return_copies(c), out, "back")
+                arena.signal(FLAG_FWD_RETURN, c, seq)
+            if c + 2 < C:
+                dispatch(c + 2)
+            recv.append(rows)
+            seg_offs.append(seg)
+            mtiles.append(mt)
+            pres.append(pre)
+            acts.append(act)
+        for c in range(C):
+            arena.wait(FLAG_FWD_RETURN, c, seq)
+        back = arena.regions["back"][: maps.rows_cap]
+        y = K.combine(back, weights, maps, T)
+
+        if any(ctx.needs_input_grad[:4]):
+            ctx.lease = arena.lease()
+        ctx.save_for_backward(back, weights, w_fc, w_proj, *recv, *pres, *acts, *seg_offs, *mtiles)
+        ctx.maps, ctx.T, ctx.plan, ctx.arena, ctx.seq = maps, T, plan, arena, seq
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        plan: PeerPlan = ctx.plan
+        arena: PeerArena = ctx.arena
+        C, ws, seq = plan.n_chunks, plan.world_size, ctx.seq
+        saved = ctx.saved_tensors
+        back, weights, w_fc, w_proj = saved[:4]
+        recv, pres, acts, seg_offs, mtiles = (saved[4 + i * C : 4 + (i + 1) * C] for i in range(5))
+        maps = ctx.maps
+        dev = dy.device
+        main, comm = torch.cuda.current_stream(dev), _comm_stream(dev)
+        need_x, need_w, need_fc, need_proj = ctx.needs_input_grad[:4]
+
+        d_back, d_w = K.combine_backward(dy.contiguous(), back, weights, maps, need_w)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        d_back.record_stream(comm)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+        d_w_fc = torch.empty_like(w_fc) if need_fc else None
+        d_w_proj = torch.empty_like(w_proj) if need_proj else None
+
+        def dispatch(c: int) -> None:
+            with torch.cuda.stream(comm):
+                arena.push(plan.dispatch_copies(c), d_back, "d_out")
+                arena.signal(FLAG_BWD_DISPATCH, c, seq)
+
+        dispatch(0)
+        if C > 1:
+            dispatch(1)
+        for c in range(C):
+            e0, e1 = plan.experts(c)
+            base, n_rows = plan.recv_chunk(c)
+            arena.wait(FLAG_BWD_DISPATCH, c, seq)
+            d_out = arena.regions["d_out"][base : base + n_rows]
+            if need_proj:
+                K.gemm_wgrad(d_out, acts[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_proj[e0:e1])
+            d_pre = K.gemm_dgrad_swiglu(d_out, w_proj[e0:e1], pres[c], mtiles[c])
+            if need_fc:
+                K.gemm_wgrad(d_pre, recv[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_fc[e0:e1])
+            d_recv = K.gemm_dgrad(d_pre, w_fc[e0:e1], mtiles[c])
+            done = torch.cuda.Event()
+            done.record(main)
+            d_recv.record_stream(comm)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                arena.push(plan.return_copies(c), d_recv, "d_xg")
+                arena.signal(FLAG_BWD_RETURN, c, seq)
+            if c + 2 < C:
+                dispatch(c + 2)
+        # every rank waits for all returns even if it needs no input gradient: the peers' pushes into
+        # this arena are then complete before the next layer call reuses it
+        for c in range(C):
+            arena.wait(FLAG_BWD_RETURN, c, seq)
+        d_x = K.scatter_backward(arena.regions["d_xg"][: maps.rows_cap], maps, ctx.T) if need_x else None
+        ctx.lease = None
+        return d_x, d_w, d_w_fc, d_w_proj, None, None, None, None

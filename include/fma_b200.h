@@ -323,6 +323,35 @@ int fma_b200_grouped_gemm(const void* A, const void* B, void* D, const uint32_t*
                           const uint32_t* K, int32_t n_groups, int32_t a_transposed, int32_t b_transposed,
                           void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ======================================================================= */
+/* peer-memory transport of the expert-parallel layer                        */
+/* ======================================================================= */
+/*
+ * No counterpart in the reference (it has no expert parallelism).  Buffers that every process of a
+ * node can address (CUDA IPC), row-block copies into them with the copy engines, and sequence-numbered
+ * flags: the sender's stream runs peer_copy then peer_signal, the receiver's stream runs peer_wait
+ * before the kernels that read the rows.
+ *
+ * peer_buffer_create  cudaMalloc + zero fill + IPC handle (FMA_B200_PEER_HANDLE_BYTES bytes) of a
+ *                     buffer on the current device.
+ * peer_buffer_open    maps another process's buffer from its handle; *ptr_out is valid in this process
+ *                     (copies and kernels of this library may write to it).  Not for one's own handle.
+ * peer_buffer_close / peer_buffer_destroy   undo open / create.
+ * peer_copy           n cudaMemcpyAsync calls dst[i] <- src[i], bytes[i] (device addresses in host
+ *                     arrays), in order, on `stream`.
+ * peer_signal         one small kernel: *flag_addrs[i] = value (release, system scope), n <= 64.
+ * peer_wait           one small kernel: returns when flags[i] - value >= 0 for all i < n, or records
+ *                     device status 0x7002 after timeout_ms (1..60000) and returns.
+ */
+#define FMA_B200_PEER_HANDLE_BYTES 64
+int fma_b200_peer_buffer_create(int64_t bytes, void** ptr_out, uint8_t* handle_out);
+int fma_b200_peer_buffer_open(const uint8_t* handle, void** ptr_out);
+int fma_b200_peer_buffer_close(void* ptr);
+int fma_b200_peer_buffer_destroy(void* ptr);
+int fma_b200_peer_copy(int32_t n, const uint64_t* dst, const uint64_t* src, const int64_t* bytes, void* stream);
+int fma_b200_peer_signal(int32_t n, const uint64_t* flag_addrs, int32_t value, void* stream);
+int fma_b200_peer_wait(const int32_t* flags, int32_t n, int32_t value, int32_t timeout_ms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

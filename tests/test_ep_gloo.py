@@ -102,3 +102,60 @@ def test_shard_and_unshard_state_dict_round_trip():
     sd = dict(shards[0])
     sd["gate.weight"] = sd["gate.weight"][:2]
     local.load_state_dict(sd, strict=True)
+
+
+@pytest.mark.parametrize("world,E,chunks,align", [(2, 8, 1, 256), (3, 12, 4, 128), (4, 64, 6, 256), (8, 128, 6, 256)])
+def test_peer_plan_routes_every_block(world, E, chunks, align):
+    """Host plan of the peer-memory transport: applying every rank's copy lists to emulated arenas
+    (numpy) must build the [chunk][source][expert] receive layout on each rank, and the return copies
+    must rebuild every sender's own grouped layout."""
+    sys.path.insert(0, str(ROOT / "cute-kernels_b200"))
+    from fma_b200.modules.moe_ep_peer import PeerPlan
+
+    rng = np.random.default_rng(world * 1000 + E)
+    counts = rng.choice([0, 1, 7, align - 1, align, align + 1, 3 * align + 5], size=(world, E)).tolist()
+    El = E // world
+    plans = [PeerPlan(counts, r, chunks, align) for r in range(world)]
+    pad = lambda n: (n + align - 1) // align * align  # noqa: E731
+
+    # every rank's grouped layout: row label = s * 1e9 + e * 1e6 + i, padding rows -1
+    def layout(s):
+        rows = []
+        for e in range(E):
+            n = counts[s][e]
+            rows += [s * 10**9 + e * 10**6 + i for i in range(n)] + [-1] * (pad(n) - n)
+        return np.array(rows, dtype=np.int64)
+
+    xg = [layout(s) for s in range(world)]
+    for s in range(world):
+        assert plans[s].total_send_rows == xg[s].size
+    recv = [np.full(plans[0].total_recv_rows[r], -7, dtype=np.int64) for r in range(world)]
+    for s in range(world):
+        for c in range(plans[s].n_chunks):
+            copies = plans[s].dispatch_copies(c)
+            assert sorted(r for r, *_ in copies) == list(range(world)) and copies[-1][0] == s
+            for r, dst, src, n in copies:
+                assert np.all(recv[r][dst : dst + n] == -7)  # no two blocks overlap
+                recv[r][dst : dst + n] = xg[s][src : src + n]
+    for r in range(world):
+        assert not np.any(recv[r] == -7)  # every row of the receive layout was written
+        for c in range(plans[r].n_chunks):
+            e0, e1 = plans[r].experts(c)
+            base, n_rows = plans[r].recv_chunk(c)
+            want = []
+            for s in range(world):
+                for e in range(r * El + e0, r * El + e1):
+                    first = sum(pad(v) for v in counts[s][:e])
+                    want.append(xg[s][first : first + pad(counts[s][e])])
+            want = np.concatenate(want) if want else np.zeros(0, np.int64)
+            assert n_rows == want.size and n_rows % 128 == 0
+            np.testing.assert_array_equal(recv[r][base : base + n_rows], want)
+    back = [np.full(xg[s].size, -7, dtype=np.int64) for s in range(world)]
+    for r in range(world):
+        for c in range(plans[r].n_chunks):
+            base, n_rows = plans[r].recv_chunk(c)
+            out = recv[r][base : base + n_rows]  # identity "experts"
+            for s, dst, src, n in plans[r].return_copies(c):
+                back[s][dst : dst + n] = out[src : src + n]
+    for s in range(world):
+        np.testing.assert_array_equal(back[s], xg[s])

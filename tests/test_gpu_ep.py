@@ -1,5 +1,6 @@
-"""Expert-parallel MoE on 2 GPUs (NCCL all-to-all) against the single-GPU layer holding all experts.
-Skipped on a box with one GPU."""
+"""Expert-parallel MoE on 2 GPUs against the single-GPU layer holding all experts, over both
+transports: copy-engine pushes into peer-mapped arenas, and NCCL all-to-all.  Skipped on a box with
+one GPU."""
 
 import socket
 import sys
@@ -43,34 +44,60 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
             full.c_fc.weight.copy_(randn((E, 2 * I, H), torch.float32, 2, 0.02))
             full.c_proj.weight.copy_(randn((E, H, I), torch.float32, 3, 0.02))
         full = full.to(dev).to(dtype)
-        ep = fma_b200.ExpertParallelMoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02)
-        shard = fma_b200.shard_expert_state_dict(full.state_dict(), rank, world)
-        ep = ep.to(dev).to(dtype)
-        ep.load_state_dict(shard, strict=True)
-
         xs = [randn((T + 64 * r, H), dtype, 10 + r).to(dev) for r in range(world)]  # ragged T per rank
         gs = [randn((T + 64 * r, H), dtype, 20 + r).to(dev) for r in range(world)]
-        x = xs[rank].clone().requires_grad_(True)
-        y, logits = ep(x)
-        y.backward(gs[rank])
-        torch.cuda.synchronize()
-
         x_all = torch.cat(xs).requires_grad_(True)
         y_all, logits_all = full(x_all)
         y_all.backward(torch.cat(gs))
         lo = sum(t.size(0) for t in xs[:rank])
         hi = lo + xs[rank].size(0)
-        assert torch.equal(logits, logits_all[lo:hi])
-        e0, e1 = ep.local_expert_range()
-        errs = {
-            "y": _rel(y, y_all[lo:hi]),
-            "dx": _rel(x.grad, x_all.grad[lo:hi]),
-            "d_w_fc": _rel(ep.c_fc.weight.grad, full.c_fc.weight.grad[e0:e1]),
-            "d_w_proj": _rel(ep.c_proj.weight.grad, full.c_proj.weight.grad[e0:e1]),
-        }
-        assert all(v <= 1e-2 for v in errs.values()), errs
-        # y is a per-token computation: the expert-parallel result matches the local one bit for bit
-        assert torch.equal(y, y_all[lo:hi])
+
+        shard = fma_b200.shard_expert_state_dict(full.state_dict(), rank, world)
+        results = {}
+        for transport in ("peer", "nccl"):
+            ep = fma_b200.ExpertParallelMoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02, overlap_chunks=3,
+                                            transport=transport)  # fmt: skip
+            ep = ep.to(dev).to(dtype)
+            ep.load_state_dict(shard, strict=True)
+            for step in range(3):  # the arena is reused from the second step on
+                for p in ep.parameters():
+                    p.grad = None
+                x = xs[rank].clone().requires_grad_(True)
+                y, logits = ep(x)
+                assert ep.last_transport == transport
+                y.backward(gs[rank])
+                torch.cuda.synchronize()
+                assert torch.equal(logits, logits_all[lo:hi])
+                e0, e1 = ep.local_expert_range()
+                errs = {
+                    "y": _rel(y, y_all[lo:hi]),
+                    "dx": _rel(x.grad, x_all.grad[lo:hi]),
+                    "d_w_fc": _rel(ep.c_fc.weight.grad, full.c_fc.weight.grad[e0:e1]),
+                    "d_w_proj": _rel(ep.c_proj.weight.grad, full.c_proj.weight.grad[e0:e1]),
+                }
+                assert all(v <= 1e-2 for v in errs.values()), (transport, step, errs)
+                # y is a per-token computation: the expert-parallel result matches the local one bit for bit
+                assert torch.equal(y, y_all[lo:hi])
+            results[transport] = (y, x.grad, ep.c_fc.weight.grad.clone(), ep.c_proj.weight.grad.clone())
+            if transport == "peer":
+                # a second forward while the first one's backward is pending must not touch the arena
+                x1 = xs[rank].clone().requires_grad_(True)
+                y1, _ = ep(x1)
+                x2 = xs[rank].clone().requires_grad_(True)
+                y2, _ = ep(x2)
+                assert ep.last_transport == "nccl"
+                y2.backward(gs[rank])
+                y1.backward(gs[rank])
+                torch.cuda.synchronize()
+                assert torch.equal(y1, y_all[lo:hi]) and torch.equal(y2, y_all[lo:hi])
+                assert torch.equal(x1.grad, x2.grad)
+                with torch.no_grad():
+                    y3, _ = ep(xs[rank])
+                assert ep.last_transport == "peer" and torch.equal(y3, y_all[lo:hi])
+                ep.close_peer_transport()
+        # both transports move the same rows into the same layouts: identical results
+        for a, b in zip(results["peer"], results["nccl"]):
+            assert torch.equal(a, b)
         from fma_b200 import _native
 
         assert _native.device_status() == 0
