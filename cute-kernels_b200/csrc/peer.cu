@@ -35,6 +35,9 @@ __global__ void peer_wait_kernel(const int32_t* __restrict__ flags, int n, int32
                                  int32_t* __restrict__ status) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
+    // once any wait has run out the exchange is broken: later waits return at once, so the step ends
+    // quickly and the host finds the status word
+    if (*reinterpret_cast<volatile const int32_t*>(status) == STATUS_PEER_TIMEOUT) return;
     uint64_t t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (;;) {

@@ -35,6 +35,8 @@ from . import _kernels as K
 from .moe import MoE, _is_swiglu_packed, _RouterTopK
 
 ROW_ALIGN = K.ROW_ALIGN
+# transport="auto" uses the peer-memory transport up to this group size and NCCL all-to-all above it.
+PEER_AUTO_MAX_RANKS = 2
 
 
 def exchange_counts(expert_count: torch.Tensor, world_size: int, group) -> torch.Tensor:
@@ -343,7 +345,9 @@ class ExpertParallelMoE(MoE):
         with torch.no_grad():
             maps = K.moe_sort(selected_experts, self.num_experts)
         self.last_row_maps = maps
-        if self.transport != "nccl" and self._peer_unavailable is None:
+        # "auto" takes the peer-memory transport only for the group size it has been validated on
+        use_peer = self.transport == "peer" or (self.transport == "auto" and self.ep_size <= PEER_AUTO_MAX_RANKS)
+        if use_peer and self._peer_unavailable is None:
             y = self._compute_experts_peer(hidden_states, router_weights, maps)
             if y is not None:
                 self.last_transport = "peer"

@@ -24,6 +24,7 @@ Arena regions (rows of H elements):
 from __future__ import annotations
 
 import ctypes
+import os
 import weakref
 
 import torch
@@ -38,7 +39,21 @@ MAX_RANKS = 64
 REGIONS = ("recv", "d_out", "back", "d_xg")
 FLAG_FWD_DISPATCH, FLAG_FWD_RETURN, FLAG_BWD_DISPATCH, FLAG_BWD_RETURN = range(4)
 FLAG_BYTES = 4 * 4 * MAX_CHUNKS * MAX_RANKS
-WAIT_TIMEOUT_MS = 4000
+# Longest time a wait kernel polls for a peer's flag before it records the timeout status and returns.
+WAIT_TIMEOUT_MS = int(os.environ.get("FMA_B200_PEER_TIMEOUT_MS", "2000"))
+
+
+_DEBUG = os.environ.get("FMA_B200_PEER_DEBUG", "0") == "1"
+
+
+def _debug(rank: int, text: str) -> None:
+    """Progress lines of the collective set-up on stderr (FMA_B200_PEER_DEBUG=1): which phase a rank is in
+    and how long the previous one took."""
+    if _DEBUG:
+        import sys
+        import time
+
+        print(f"[fma_b200 peer rank {rank} t={time.monotonic():.3f}] {text}", file=sys.stderr, flush=True)
 
 
 class PeerTransportUnavailable(RuntimeError):
@@ -142,6 +157,7 @@ class PeerArena:
         with torch.cuda.device(device):
             # every phase ends in a collective that all ranks reach, whether their part worked or not
             error = None
+            _debug(self.rank, f"creating an arena of {self.nbytes >> 20} MiB")
             try:
                 _native.call("fma_b200_peer_buffer_create", self.nbytes, ctypes.byref(local), handle)
                 self.local_ptr = int(local.value)
@@ -150,6 +166,7 @@ class PeerArena:
             created = [None] * self.world_size
             dist.all_gather_object(created, (error, bytes(handle)), group=group)
             opened: list[int] = []
+            _debug(self.rank, "arena created and handles gathered; mapping the peers' arenas")
             if error is None and all(err is None for err, _ in created):
                 try:
                     for r, (_, h) in enumerate(created):
@@ -176,6 +193,7 @@ class PeerArena:
                     self.local_ptr = 0
                 raise PeerTransportUnavailable("; ".join(f"rank {r}: {e}" for r, e in enumerate(errors) if e))
             self.peer_ptrs = opened
+            _debug(self.rank, f"{len(opened) - 1} peer arenas mapped")
         raw = torch.as_tensor(_RawCudaMemory(self.local_ptr, self.nbytes), device=device)
         self.flags = raw[:FLAG_BYTES].view(torch.int32)
         self.regions = {
