@@ -167,6 +167,35 @@ def layer_step(layer, x, dy):
     return y
 
 
+def write_timeline(path: str, step, rank: int, barrier) -> None:
+    """One step under torch.profiler (kineto) on rank 0, the other ranks run it plainly; the file lists
+    every device activity in start order.  Shows what overlaps what (GEMMs, exchanges, waits); durations
+    under the profiler are not benchmark numbers."""
+    barrier()
+    if rank != 0:
+        step()
+        barrier()
+        return
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    with tempfile.TemporaryDirectory() as tmp:
+        raw = os.path.join(tmp, "trace.json")
+        prof.export_chrome_trace(raw)
+        with open(raw) as f:
+            events = json.load(f)["traceEvents"]
+    acts = sorted((e for e in events if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset")), key=lambda e: e["ts"])
+    t0 = acts[0]["ts"] if acts else 0
+    with open(path, "w") as f:
+        f.write("# start_ms duration_ms stream name\n")
+        for e in acts:
+            f.write("%9.3f %8.3f s%-3s %s\n" % ((e["ts"] - t0) / 1e3, e["dur"] / 1e3, e["args"].get("stream", "?"),
+                                               e["name"][:90]))  # fmt: skip
+    barrier()
+
+
 # ---------------------------------------------------------------------------------------------
 # algorithmic work (what roofline figures are computed from)
 # ---------------------------------------------------------------------------------------------
@@ -379,6 +408,10 @@ def main() -> None:
     ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--timeline", default="", metavar="FILE",
+                    help="after the timed runs, record one more step with torch.profiler on rank 0 and write its "
+                         "device timeline (start ms, duration ms, stream, kernel or copy) to FILE; never part of a "
+                         "reported number")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.tokens else args.warmup
     peaks, peaks_kind = load_peaks()
@@ -546,6 +579,9 @@ def main() -> None:
                     else "gemm_simt_kernel",
                     "peak_kind": f"{peaks_kind} sustained cuBLAS bf16", "gemm_ms_per_step": gemm_ms,
                     "gemm_share_of_step": gemm_ms / ms_step}  # fmt: skip
+
+    if args.timeline:
+        write_timeline(args.timeline, lambda: layer_step(layer, x, dy), rank, barrier)
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
