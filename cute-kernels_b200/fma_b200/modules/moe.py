@@ -221,6 +221,8 @@ class MoE(nn.Module):
         )
 
         self.act = activation_function
+        # decided once, outside any compiled region: can the activation run inside the GEMM epilogue?
+        self._act_is_swiglu_packed = _is_swiglu_packed(activation_function)
 
         self.c_proj = Experts(
             num_experts=num_experts,
@@ -240,12 +242,27 @@ class MoE(nn.Module):
         _native.require_cuda(hidden_states)
         original_shape = hidden_states.shape
         hidden_states = hidden_states.reshape(-1, self.hidden_size)
+        if torch.compiler.is_compiling():
+            return self._forward_traced(hidden_states, original_shape)
 
         with torch.cuda.device(hidden_states.device):
             router_logits, router_weights, selected_experts = self._compute_routing_weights(hidden_states)
             hidden_states = self._compute_experts(hidden_states, router_weights, selected_experts)
 
         return hidden_states.view(original_shape), router_logits
+
+    def _forward_traced(self, hidden_states: torch.Tensor, original_shape) -> tuple[torch.Tensor, torch.Tensor]:
+        """The same layer through torch.library custom ops (`_moe_ops`), for torch.compile(fullgraph=True):
+        no Python object crosses an op boundary and nothing is stored on the module."""
+        from . import _moe_ops
+
+        if not (self.is_glu and self._act_is_swiglu_packed and self.c_fc.bias is None and self.c_proj.bias is None):
+            raise NotImplementedError("torch.compile covers MoE with swiglu_packed experts and no bias")
+        router_logits = self.gate(hidden_states)
+        router_weights, selected_experts = _moe_ops.moe_route(router_logits, self.top_k)
+        outputs = _moe_ops.moe_swiglu_experts(hidden_states, router_weights, selected_experts, self.c_fc.weight,
+                                              self.c_proj.weight, K.ROW_ALIGN)  # fmt: skip
+        return outputs[0].view(original_shape), router_logits
 
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
         router_logits = self.gate(hidden_states)

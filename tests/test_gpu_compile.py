@@ -58,3 +58,40 @@ def test_grouped_gemm_compiled():
              output_shape=(sum(Ms) * N,), is_A_transposed=False, is_B_transposed=True)
     want = torch.cat([(a.float() @ b.float().T).to(torch.bfloat16).reshape(-1) for a, b in zip(As, Bs)])
     assert torch.equal(out.cpu(), want)
+
+
+def test_moe_layer_compiled_fullgraph():
+    """The whole layer under torch.compile(fullgraph=True), forward and backward, as the reference compiles
+    its MoE (tests/modules/moe_test.py:97-98): same kernels in the same order as the eager path."""
+    import fma_b200
+    from fma_b200 import _native
+
+    T, H, E, k, I = 384, 256, 8, 2, 128
+    dtype = torch.bfloat16
+    moe = fma_b200.MoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02)
+    with torch.no_grad():
+        moe.gate.weight.copy_(randn((E, H), torch.float32, 1, 0.02))
+        moe.c_fc.weight.copy_(randn((E, 2 * I, H), torch.float32, 2, 0.02))
+        moe.c_proj.weight.copy_(randn((E, H, I), torch.float32, 3, 0.02))
+    moe = moe.to(DEV).to(dtype)
+    x = randn((3, T // 3, H), dtype, 4).to(DEV)
+    g = randn((3, T // 3, H), dtype, 5).to(DEV)
+
+    def run(fn):
+        for p in moe.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        y, logits = fn(xi)
+        y.backward(g)
+        return [y.detach(), logits.detach(), xi.grad] + [p.grad.clone() for p in moe.parameters()]
+
+    eager = run(moe)
+    compiled = run(torch.compile(moe, fullgraph=True))
+    assert _native.device_status() == 0
+    assert compiled[0].shape == x.shape and compiled[1].shape == (T, E)
+    if torch.equal(eager[1], compiled[1]):  # same logits -> same routing -> same kernels on the same data
+        for a, b in zip(eager, compiled):
+            assert torch.equal(a, b)
+    else:  # the compiler chose another GEMM for the router: near-ties may route differently
+        for a, b in zip(eager, compiled):
+            assert float((a.float() - b.float()).norm() / b.float().norm()) <= 1e-2
