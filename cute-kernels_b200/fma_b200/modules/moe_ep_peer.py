@@ -43,6 +43,8 @@ FLAG_BYTES = 4 * 4 * MAX_CHUNKS * MAX_RANKS
 WAIT_TIMEOUT_MS = int(os.environ.get("FMA_B200_PEER_TIMEOUT_MS", "2000"))
 
 
+# Where the arena comes from: "ipc" = cudaMalloc + CUDA IPC through this library, "symm" = torch symmetric memory.
+ARENA_ALLOCATOR = os.environ.get("FMA_B200_PEER_ALLOC", "ipc")
 _DEBUG = os.environ.get("FMA_B200_PEER_DEBUG", "0") == "1"
 
 
@@ -152,6 +154,24 @@ class PeerArena:
         self._lease = None
 
         self.local_ptr, self.peer_ptrs = 0, []
+        self._symm = None  # (tensor, handle) when the arena comes from torch's symmetric memory
+        if ARENA_ALLOCATOR == "symm":
+            self._allocate_symm()
+        else:
+            self._allocate_ipc()
+        raw = torch.as_tensor(_RawCudaMemory(self.local_ptr, self.nbytes), device=device)
+        self.flags = raw[:FLAG_BYTES].view(torch.int32)
+        self.regions = {
+            name: raw[self.region_off[name] : self.region_off[name] + caps[name] * self.row_bytes].view(dtype).view(
+                caps[name], hidden)
+            for name in REGIONS
+        }  # fmt: skip
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def _allocate_ipc(self) -> None:
+        """cudaMalloc + CUDA IPC handles through the library's own entry points."""
+        group, device = self.group, self.device
         local = ctypes.c_void_p()
         handle = (ctypes.c_uint8 * 64)()
         with torch.cuda.device(device):
@@ -194,15 +214,26 @@ class PeerArena:
                 raise PeerTransportUnavailable("; ".join(f"rank {r}: {e}" for r, e in enumerate(errors) if e))
             self.peer_ptrs = opened
             _debug(self.rank, f"{len(opened) - 1} peer arenas mapped")
-        raw = torch.as_tensor(_RawCudaMemory(self.local_ptr, self.nbytes), device=device)
-        self.flags = raw[:FLAG_BYTES].view(torch.int32)
-        self.regions = {
-            name: raw[self.region_off[name] : self.region_off[name] + caps[name] * self.row_bytes].view(dtype).view(
-                caps[name], hidden)
-            for name in REGIONS
-        }  # fmt: skip
-        torch.cuda.synchronize(device)
-        dist.barrier(group)
+
+    def _allocate_symm(self) -> None:
+        """Arena from torch.distributed._symmetric_memory (driver virtual-memory API, handles passed between
+        the processes by torch): no CUDA IPC handles are involved.  Opt-in (FMA_B200_PEER_ALLOC=symm)."""
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = self.group if self.group is not None else dist.group.WORLD
+        _debug(self.rank, f"allocating a symmetric arena of {self.nbytes >> 20} MiB")
+        try:
+            with torch.cuda.device(self.device):
+                tensor = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+                handle = symm_mem.rendezvous(tensor, group)
+                tensor.zero_()
+        except Exception as e:  # every rank fails or none: rendezvous is collective
+            raise PeerTransportUnavailable(f"symmetric memory: {e}") from e
+        self._symm = (tensor, handle)
+        self.local_ptr = tensor.data_ptr()
+        self.peer_ptrs = [int(p) for p in handle.buffer_ptrs]
+        self.peer_ptrs[self.rank] = self.local_ptr
+        _debug(self.rank, "symmetric arena mapped")
 
     # ---- lifetime ---------------------------------------------------------------------------
     def lease(self):
@@ -225,6 +256,11 @@ class PeerArena:
             return
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
+        if self._symm is not None:
+            self.flags, self.regions, self._symm = None, {}, None
+            self.local_ptr, self.peer_ptrs = 0, []
+            dist.barrier(self.group)
+            return
         with torch.cuda.device(self.device):
             for r, p in enumerate(self.peer_ptrs):
                 if r != self.rank:

@@ -53,6 +53,22 @@ def test_status_strings_and_bad_arguments_without_gpu():
     assert lib.fma_b200_moe_rows_cap(1000, 8, 256) == 3072
     assert lib.fma_b200_moe_rows_cap(0, 1, 128) == 128
     assert lib.fma_b200_continuous_count_workspace_bytes(128) == 128 + 8 * 128 * 4
+    # expert bias and the peer-memory transport
+    assert lib.fma_b200_moe_bias_add(null, null, 7, 128, 64, null, null, null) == 2  # dtype
+    assert lib.fma_b200_moe_bias_add(null, null, 1, 128, 12, null, null, null) == 1  # width not 16-byte multiple
+    assert lib.fma_b200_moe_bias_add(null, null, 1, 0, 64, null, null, null) == 0  # nothing to do
+    assert lib.fma_b200_moe_bias_grad(null, 1, 0, 64, null, null, null) == 1  # E < 1
+    assert lib.fma_b200_peer_buffer_create(0, null, null) == 1
+    assert lib.fma_b200_peer_buffer_open(null, null) == 1
+    assert lib.fma_b200_peer_copy(0, null, null, null, null) == 0
+    assert lib.fma_b200_peer_copy(-1, null, null, null, null) == 1
+    one = (ctypes.c_uint64 * 1)(0)
+    assert lib.fma_b200_peer_copy(1, one, one, (ctypes.c_int64 * 1)(16), null) == 1  # NULL address
+    assert lib.fma_b200_peer_signal(65, one, 1, null) == 1  # more than 64 flags
+    assert lib.fma_b200_peer_signal(1, one, 1, null) == 1  # NULL flag address
+    assert lib.fma_b200_peer_wait(null, 1, 1, 1000, null) == 1
+    assert lib.fma_b200_peer_wait(one, 1, 1, 0, null) == 1  # no unbounded waits
+    assert lib.fma_b200_peer_wait(one, 1, 1, 600000, null) == 1
 
 
 def test_python_surface_matches_reference_names():
