@@ -408,6 +408,10 @@ def main() -> None:
     ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-prefetch", action="store_true",
+                    help="end-to-end loop as a streaming input pipeline: the host-to-device copy of step i+1 and the "
+                         "device-to-host copy of step i's input gradient overlap the neighbouring step's kernels "
+                         "(every copy still lies inside the timed region)")
     ap.add_argument("--timeline", default="", metavar="FILE",
                     help="after the timed runs, record one more step with torch.profiler on rank 0 and write its "
                          "device timeline (start ms, duration ms, stream, kernel or copy) to FILE; never part of a "
@@ -525,14 +529,62 @@ def main() -> None:
             dx_host.copy_(xd.grad, non_blocking=True)
             main_stream.wait_stream(copy_stream)  # the step ends when every copy has landed
 
-        for _ in range(2):
-            e2e_step()
+        out_stream = torch.cuda.Stream(device)
+
+        def e2e_loop_prefetch(n_steps: int) -> None:
+            """Same copies and kernels as n_steps calls of e2e_step, as a streaming pipeline: inputs of step
+            i+1 travel on copy_stream while step i computes; y and the input gradient go back on out_stream
+            while the next kernels run.  The loop ends when the last copy has landed."""
+
+            def issue_inputs():
+                with torch.cuda.stream(copy_stream):
+                    xd = x_host.to(device, non_blocking=True)
+                    dyd = dy_host.to(device, non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(copy_stream)
+                return xd, dyd, ready
+
+            nxt = issue_inputs()
+            for i in range(n_steps):
+                xd, dyd, ready = nxt
+                if i + 1 < n_steps:
+                    nxt = issue_inputs()
+                for p in layer.parameters():
+                    p.grad = None
+                main_stream.wait_event(ready)
+                xd.record_stream(main_stream)
+                dyd.record_stream(main_stream)
+                xd.requires_grad_(True)
+                y, _ = layer(xd)
+                y_ready = torch.cuda.Event()
+                y_ready.record(main_stream)
+                with torch.cuda.stream(out_stream):
+                    out_stream.wait_event(y_ready)
+                    y_host.copy_(y.detach(), non_blocking=True)
+                    y.record_stream(out_stream)
+                y.backward(dyd)
+                dx = xd.grad
+                dx_ready = torch.cuda.Event()
+                dx_ready.record(main_stream)
+                with torch.cuda.stream(out_stream):
+                    out_stream.wait_event(dx_ready)
+                    dx_host.copy_(dx, non_blocking=True)
+                    dx.record_stream(out_stream)
+            main_stream.wait_stream(out_stream)
+
+        def e2e_run(n_steps: int) -> None:
+            if args.e2e_prefetch:
+                e2e_loop_prefetch(n_steps)
+            else:
+                for _ in range(n_steps):
+                    e2e_step()
+
+        e2e_run(2)
         barrier()
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        for _ in range(args.steps):
-            e2e_step()
+        e2e_run(args.steps)
         t1.record()
         barrier()
         e2e_ms = t0.elapsed_time(t1)
@@ -542,7 +594,8 @@ def main() -> None:
             e2e_ms = float(t.item())
         nbytes = x_host.numel() * x_host.element_size()
         e2e = {"value": world * T / (e2e_ms / args.steps / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
-               "d2h_bytes_per_step": 2 * nbytes, "ms_per_step": e2e_ms / args.steps}  # fmt: skip
+               "d2h_bytes_per_step": 2 * nbytes, "ms_per_step": e2e_ms / args.steps,
+               "pipeline": "inputs of step i+1 prefetched during step i" if args.e2e_prefetch else "per-step copies"}  # fmt: skip
 
     if rank != 0:
         if world > 1:
