@@ -17,11 +17,11 @@ int tc_general(const void* A, const void* B, void* D, const uint32_t* M, const u
                int n_groups, bool a_t, bool b_t, void* workspace, int64_t workspace_bytes, cudaStream_t s);
 int64_t tc_general_workspace_bytes(int n_groups, int64_t total_mtiles);
 int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-                const int32_t* mtile_expert, cudaStream_t s);
+                const int32_t* mtile_expert, bool narrow, cudaStream_t s);
 int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                       const int32_t* mtile_expert, cudaStream_t s);
+                       const int32_t* mtile_expert, bool narrow, cudaStream_t s);
 int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* mtile_expert, bool swiglu, cudaStream_t s);
+              const int32_t* mtile_expert, bool swiglu, bool narrow, cudaStream_t s);
 int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
               const int32_t* seg_offsets, int n_seg, cudaStream_t s);
 int simt_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
@@ -42,9 +42,21 @@ static bool use_pairs(int32_t row_align) {
     return enabled == 1 && row_align > 0 && row_align % 256 == 0;
 }
 
+// Measurement knob FMA_B200_GEMM_NARROW (bit mask, default 0 = off): the pair kernels with 256x256 tiles whose
+// two tensor-memory halves belong to consecutive tiles.  Bit 0: the two SwiGLU-epilogue GEMMs (which then run
+// on CTA pairs), bit 1: the plain forward GEMM, bit 2: the plain dgrad GEMM.
+static int narrow_mask() {
+    static int v = -1;
+    if (v < 0) {
+        const char* env = getenv("FMA_B200_GEMM_NARROW");
+        v = env ? (atoi(env) & 7) : 0;
+    }
+    return v;
+}
+
 static bool pairs_for_fused_epilogues() {
     const char* env = getenv("FMA_B200_GEMM_PAIRS");
-    return env != nullptr && atoi(env) == 2;
+    return (env != nullptr && atoi(env) == 2) || (narrow_mask() & 1);
 }
 
 static int check_layer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN) {
@@ -69,7 +81,8 @@ int fma_b200_moe_gemm_forward(const void* X, const void* W, void* Y, int32_t dty
     FMAB_REQUIRE(X && W && Y && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(X) && aligned16(W) && aligned16(Y), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_BF16 && use_pairs(row_align)) return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
+    if (dtype == FMA_B200_BF16 && use_pairs(row_align))
+        return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, (narrow_mask() & 2) != 0, s);
     if (dtype == FMA_B200_BF16) return tc_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
     return simt_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
 }
@@ -83,7 +96,7 @@ int fma_b200_moe_gemm_dgrad(const void* dY, const void* W, void* dX, int32_t dty
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(dX), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == FMA_B200_BF16 && use_pairs(row_align))
-        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, s);
+        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, (narrow_mask() & 4) != 0, s);
     if (dtype == FMA_B200_BF16) return tc_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, s);
     return simt_dgrad(dY, W, dX, rows_cap, E, OUT, IN, mtile_expert, s);
 }
@@ -117,7 +130,8 @@ int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, vo
     // The SwiGLU epilogues are long; they run on the single-CTA kernel, whose two accumulators belong to
     // different tiles so that an epilogue overlaps the next tile's main loop (FMA_B200_GEMM_PAIRS=2 forces pairs).
     if (use_pairs(row_align) && pairs_for_fused_epilogues())
-        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, static_cast<cudaStream_t>(stream));
+        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, (narrow_mask() & 1) != 0,
+                                  static_cast<cudaStream_t>(stream));
     return tc_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, static_cast<cudaStream_t>(stream));
 }
 
@@ -133,7 +147,8 @@ int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pr
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(pre) && aligned16(d_pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
     if (use_pairs(row_align) && pairs_for_fused_epilogues())
-        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, static_cast<cudaStream_t>(stream));
+        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, (narrow_mask() & 1) != 0,
+                         static_cast<cudaStream_t>(stream));
     return tc_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, static_cast<cudaStream_t>(stream));
 }
 

@@ -1,4 +1,5 @@
-// bf16 grouped GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256x512 output tile per pair of SMs.
+// bf16 grouped GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256x512 output tile per pair of SMs
+// (HALVES = 2, described below; HALVES = 1 is the 256x256 variant, see PairShape).
 //
 // Why pairs: a 128x256x16 MMA issued by one CTA reads 12 KB of shared memory per 128 tensor-pipe
 // cycles while TMA writes the next operands at the same rate, which together exceed what the
@@ -36,14 +37,21 @@
 
 namespace fmab {
 
-constexpr int PAIR_STAGES = 4;
-constexpr int PAIR_HALVES = 2;                                      // 256-column accumulator halves per tile
 constexpr int PAIR_B_ROWS = BN / 2;                                 // B rows staged per CTA and half (128)
 constexpr int PAIR_B_BYTES = PAIR_B_ROWS * BK * 2;                  // 16 KB
-constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_HALVES * PAIR_B_BYTES;  // 16 KB + 2 x 16 KB
 constexpr int PAIR_THREADS = 320;
 constexpr int PAIR_EPI_WARPS = 8;
-constexpr size_t PAIR_SMEM_BYTES = static_cast<size_t>(PAIR_STAGES) * PAIR_STAGE_BYTES + 1024;
+
+// Shape of a pair tile.  HALVES = 2: 256 rows x 512 columns, both 256-column halves of tensor memory belong
+// to ONE tile (A staged once for two halves).  HALVES = 1: 256 rows x 256 columns, the two halves of tensor
+// memory belong to CONSECUTIVE tiles, so a whole epilogue overlaps the next tile's main loop (for long
+// epilogues and short reductions); stages are smaller, so the ring is deeper.
+template <int HALVES>
+struct PairShape {
+    static constexpr int kStages = (HALVES == 2) ? 4 : 6;
+    static constexpr int kStageBytes = A_STAGE_BYTES + HALVES * PAIR_B_BYTES;  // 16 KB + HALVES x 16 KB
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -130,7 +138,7 @@ struct PairTile {
 };
 
 // tile -> (pair m-tile, n-tile) with SUPER_M/2 pair m-tiles walked together
-template <bool B_MN, int EPI>
+template <bool B_MN, int EPI, int HALVES>
 __device__ __forceinline__ bool decode_pair_tile(const GemmParams& p, int tile, int n_pair_mtiles, uint32_t rank, PairTile& t) {
     constexpr int kSuper = SUPER_M / 2;
     const int per_super = kSuper * p.n_ntiles;
@@ -141,9 +149,9 @@ __device__ __forceinline__ bool decode_pair_tile(const GemmParams& p, int tile, 
     const int nt = r / m_span;
     const int pm = m_first + (r - nt * m_span);
     constexpr int n_step = (EPI == EPI_SWIGLU_FWD) ? BN / 2 : BN;
-    t.n0 = nt * PAIR_HALVES * n_step;
+    t.n0 = nt * HALVES * n_step;
     t.n_step = n_step;
-    t.halves = (t.n0 + n_step < p.n_cols) ? 2 : 1;
+    t.halves = (HALVES == 2 && t.n0 + n_step < p.n_cols) ? 2 : 1;
     t.b_k_base = 0;
     if (p.mode == MODE_ROWS) {
         const int e = __ldg(p.mtile_expert + 2 * pm);  // both 128-row tiles of the pair belong to this expert
@@ -188,9 +196,11 @@ __device__ __forceinline__ void decode_pair_segment(const GemmParams& p, const P
     }
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, int HALVES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
+    constexpr int PAIR_STAGES = PairShape<HALVES>::kStages;
+    constexpr int PAIR_STAGE_BYTES = PairShape<HALVES>::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[PAIR_STAGES];   // used in the leader only
     __shared__ __align__(8) uint64_t empty_bar[PAIR_STAGES];  // each CTA waits on its own copy
@@ -284,7 +294,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 }
                 if (tile >= total_tiles) break;
                 PairTile t;
-                if (decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) {
+                if (decode_pair_tile<B_MN, EPI, HALVES>(p, tile, n_pair_mtiles, rank, t)) {
                 for (int s = 0; s < n_seg && alive; ++s) {
                     int a_k0, b_k0, len;
                     decode_pair_segment(p, t, s, a_k0, b_k0, len);
@@ -336,6 +346,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_phase = 0;
+            uint32_t tile_count = 0;  // tiles that reached the accumulators (HALVES == 1 alternates halves)
             bool alive = true;
             int sslot = 0;
             uint32_t sphase = 0;
@@ -349,7 +360,11 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 }
                 if (tile < 0) break;
                 PairTile t;
-                if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+                if (!decode_pair_tile<B_MN, EPI, HALVES>(p, tile, n_pair_mtiles, rank, t)) continue;
+                // accumulator half and barrier parity of the "half 0" work: with HALVES == 1 tile n uses half
+                // n & 1, whose barriers complete a phase every second tile
+                const int h0 = (HALVES == 1) ? static_cast<int>(tile_count & 1u) : 0;
+                const uint32_t ph0 = (HALVES == 1) ? ((tile_count >> 1) & 1u) : acc_phase;
                 // k-blocks of the tile (all segments); only their count matters to this warp
                 int nkb = 0;
                 for (int s = 0; s < n_seg; ++s) {
@@ -370,7 +385,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         }
                         tc_fence_after();
                         if (step == 0) {
-                            if (!mbar_wait(smem_u32(&acc_empty_bar[0]), acc_phase ^ 1u, abort_ptr, p.status)) {
+                            if (!mbar_wait(smem_u32(&acc_empty_bar[h0]), ph0 ^ 1u, abort_ptr, p.status)) {
                                 alive = false;
                                 break;
                             }
@@ -381,9 +396,9 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         const uint64_t b_desc = make_smem_desc<B_MN>(sa + A_STAGE_BYTES);
 #pragma unroll
                         for (int ks = 0; ks < BK / UMMA_K; ++ks)
-                            tc_mma_pair(tmem_base, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
+                            tc_mma_pair(tmem_base + h0 * BN, a_desc + ((ks * desc_k_step<A_MN>()) >> 4),
                                         b_desc + ((ks * desc_k_step<B_MN>()) >> 4), idesc, (step | ks) ? 1u : 0u);
-                        if (step == nkb - 1) tc_commit_pair(smem_u32(&acc_full_bar[0]));
+                        if (step == nkb - 1) tc_commit_pair(smem_u32(&acc_full_bar[h0]));
                     }
                     const int kb1 = step - skew;  // k-block of half 1 in this step
                     if (kb1 >= 0) {
@@ -420,22 +435,25 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     if (t.halves == 2) tc_commit_pair(smem_u32(&acc_full_bar[1]));
                 } else {  // empty reduction: both epilogues write zeros
                     for (int h = 0; h < t.halves && alive; ++h) {
-                        if (!mbar_wait(smem_u32(&acc_empty_bar[h]), acc_phase ^ 1u, abort_ptr, p.status)) {
+                        const int hb = (HALVES == 1) ? h0 : h;
+                        const uint32_t phb = (HALVES == 1) ? ph0 : acc_phase;
+                        if (!mbar_wait(smem_u32(&acc_empty_bar[hb]), phb ^ 1u, abort_ptr, p.status)) {
                             alive = false;
                             break;
                         }
-                        mbar_arrive(smem_u32(&acc_full_bar[h]));
-                        mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[h]), 1));
+                        mbar_arrive(smem_u32(&acc_full_bar[hb]));
+                        mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[hb]), 1));
                     }
                     if (!alive) break;
                 }
-                if (t.halves == 1) {
+                if (HALVES == 2 && t.halves == 1) {
                     // keep half 1's barriers in step with the tile count: pass its phase through unused
                     if (!mbar_wait(smem_u32(&acc_empty_bar[1]), acc_phase ^ 1u, abort_ptr, p.status)) break;
                     mbar_arrive(smem_u32(&acc_full_bar[1]));
                     mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[1]), 1));
                 }
                 acc_phase ^= 1u;
+                ++tile_count;
             }
         }
     } else {
@@ -444,6 +462,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
         const int half = (warp - 2) >> 2;
         const int row_in_tile = quad * 32 + lane;
         uint32_t acc_phase = 0;
+        uint32_t tile_count = 0;
         int sslot = 0;
         uint32_t sphase = 0;
         while (true) {
@@ -457,7 +476,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             }
             if (tile < 0) break;
             PairTile t;
-            if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+            if (!decode_pair_tile<B_MN, EPI, HALVES>(p, tile, n_pair_mtiles, rank, t)) continue;
             bool any_k = false;
             for (int s = 0; s < n_seg; ++s) {
                 int a_k0, b_k0, len;
@@ -467,13 +486,16 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             const bool row_ok = row_in_tile < t.rows_valid;
             const int64_t grow = t.d_row + row_in_tile;
             bool alive = true;
-            for (int h = 0; h < PAIR_HALVES; ++h) {
-            if (!mbar_wait(smem_u32(&acc_full_bar[h]), acc_phase, abort_ptr, p.status)) {
+            for (int h = 0; h < HALVES; ++h) {
+            // tensor-memory half and barrier parity of this part of the tile (see the MMA warp)
+            const int hs = (HALVES == 1) ? static_cast<int>(tile_count & 1u) : h;
+            const uint32_t phs = (HALVES == 1) ? ((tile_count >> 1) & 1u) : acc_phase;
+            if (!mbar_wait(smem_u32(&acc_full_bar[hs]), phs, abort_ptr, p.status)) {
                 alive = false;
                 break;
             }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + h * BN + (static_cast<uint32_t>(quad * 32) << 16);
+            const uint32_t taddr = tmem_base + hs * BN + (static_cast<uint32_t>(quad * 32) << 16);
             const int n0h = t.n0 + h * t.n_step;                 // first D column of this half
             const int n_valid = min(t.n_step, p.n_cols - n0h);   // <= 0: the half carries no columns
 
@@ -561,10 +583,11 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty_bar[h]), 0));  // the leader's barrier
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty_bar[hs]), 0));  // the leader's barrier
             }  // halves
             if (!alive) break;
             acc_phase ^= 1u;
+            ++tile_count;
         }
     }
 
@@ -601,10 +624,11 @@ static int pair_skew() {
     return v;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, int HALVES = 2>
 static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s) {
     static bool configured = false;
-    auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI>;
+    auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI, HALVES>;
+    constexpr size_t PAIR_SMEM_BYTES = PairShape<HALVES>::kSmemBytes;
     if (!configured) {
         FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM_BYTES));
         configured = true;
@@ -630,7 +654,7 @@ static int fill_pair_common(GemmParams& p) {
 }
 
 int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-                const int32_t* mtile_expert, cudaStream_t s) {
+                const int32_t* mtile_expert, bool narrow, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
     if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
@@ -640,16 +664,19 @@ int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, 
     p.d = static_cast<__nv_bfloat16*>(Y);
     p.ldd = OUT;
     p.n_mtiles = static_cast<int>(rows_cap / BM);
-    p.n_ntiles = (OUT + 2 * BN - 1) / (2 * BN);
+    const int tile_cols = narrow ? BN : 2 * BN;
+    p.n_ntiles = (OUT + tile_cols - 1) / tile_cols;
     p.n_cols = OUT;
     p.k_len = IN;
     p.b_group_stride = OUT;
     p.n_groups = E;
-    return launch_pair<false, false, EPI_PLAIN>(p, static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles, s);
+    const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
+    if (narrow) return launch_pair<false, false, EPI_PLAIN, 1>(p, total, s);
+    return launch_pair<false, false, EPI_PLAIN>(p, total, s);
 }
 
 int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                       const int32_t* mtile_expert, cudaStream_t s) {
+                       const int32_t* mtile_expert, bool narrow, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
     if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
@@ -661,16 +688,19 @@ int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64
     p.ldd = I;
     p.inter = I;
     p.n_mtiles = static_cast<int>(rows_cap / BM);
-    p.n_ntiles = (I + BN - 1) / BN;  // 2 halves of 128 act columns
+    const int tile_cols = narrow ? BN / 2 : BN;  // 128 act columns per accumulator half
+    p.n_ntiles = (I + tile_cols - 1) / tile_cols;
     p.n_cols = I;
     p.k_len = IN;
     p.b_group_stride = 2 * I;
     p.n_groups = E;
-    return launch_pair<false, false, EPI_SWIGLU_FWD>(p, static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles, s);
+    const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
+    if (narrow) return launch_pair<false, false, EPI_SWIGLU_FWD, 1>(p, total, s);
+    return launch_pair<false, false, EPI_SWIGLU_FWD>(p, total, s);
 }
 
 int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* mtile_expert, bool swiglu, cudaStream_t s) {
+              const int32_t* mtile_expert, bool swiglu, bool narrow, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
     if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
@@ -682,12 +712,17 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     p.ldd = swiglu ? 2 * static_cast<int64_t>(IN) : IN;
     p.inter = IN;
     p.n_mtiles = static_cast<int>(rows_cap / BM);
-    p.n_ntiles = (IN + 2 * BN - 1) / (2 * BN);
+    const int tile_cols = narrow ? BN : 2 * BN;
+    p.n_ntiles = (IN + tile_cols - 1) / tile_cols;
     p.n_cols = IN;
     p.k_len = OUT;
     p.b_group_stride = OUT;
     p.n_groups = E;
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
+    if (narrow) {
+        if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD, 1>(p, total, s);
+        return launch_pair<false, true, EPI_PLAIN, 1>(p, total, s);
+    }
     if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD>(p, total, s);
     return launch_pair<false, true, EPI_PLAIN>(p, total, s);
 }
