@@ -85,7 +85,7 @@ def run_layer(fma, T, H, E, k, I, dtype, seed, add_bias=False):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds fma/)")
     ap.add_argument("--only-bias", action="store_true", help="write only the add_bias=True layer fixtures")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
