@@ -30,9 +30,8 @@ from typing import Callable
 import torch
 import torch.distributed as dist
 
-from ..kernel_backend import KernelBackend
 from . import _kernels as K
-from .moe import MoE, _is_swiglu_packed, _RouterTopK
+from .moe import MoE, _is_swiglu_packed
 
 ROW_ALIGN = K.ROW_ALIGN
 # transport="auto" uses the peer-memory transport up to this group size and NCCL all-to-all above it.

@@ -3,7 +3,6 @@ computation and row all-to-all (fma_b200.modules.moe_ep) on padded grouped layou
 oracle standing in for the CUDA kernels, and must reproduce the single-process oracle output for
 their own tokens."""
 
-import os
 import socket
 import sys
 from pathlib import Path
