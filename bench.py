@@ -408,6 +408,9 @@ def main() -> None:
     ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ep-fuse-return", action="store_true",
+                    help="peer transport: the down projection and the dgrad store their tiles straight into the "
+                         "senders' arenas (no return copies)")
     ap.add_argument("--e2e-prefetch", action="store_true",
                     help="end-to-end loop as a streaming input pipeline: the host-to-device copy of step i+1 and the "
                          "device-to-host copy of step i's input gradient overlap the neighbouring step's kernels "
@@ -464,6 +467,7 @@ def main() -> None:
     if world > 1:
         layer.overlap_chunks = args.ep_chunks
         layer.transport = args.ep_transport
+        layer.fuse_return = args.ep_fuse_return
     x, dy = make_inputs(cfg, rank, device, dtype)
     x.requires_grad_(True)
     T = cfg["T"]
@@ -653,7 +657,8 @@ def main() -> None:
                    "tokens_per_gpu": T, "router": cfg["router"],
                    "parallelism": f"ep{world}" if world > 1 else "single",
                    "ep_chunks": args.ep_chunks if world > 1 else None,
-                   "ep_transport": layer.last_transport if world > 1 else None, "sm_reserve": args.sm_reserve if world > 1 else None,
+                   "ep_transport": layer.last_transport if world > 1 else None,
+                   "ep_fuse_return": bool(args.ep_fuse_return) if world > 1 else None, "sm_reserve": args.sm_reserve if world > 1 else None,
                    "l2": "inputs larger than L2 (x alone is %d MB)" % (x.numel() * x.element_size() >> 20)},
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": launches,

@@ -24,6 +24,10 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
               const int32_t* mtile_expert, bool swiglu, bool narrow, cudaStream_t s);
 int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
               const int32_t* seg_offsets, int n_seg, cudaStream_t s);
+int tc2_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
+                     const int32_t* mtile_expert, cudaStream_t s);
+int tc2_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
+                   const int32_t* mtile_expert, cudaStream_t s);
 int simt_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
                  const int32_t* mtile_expert, cudaStream_t s);
 int simt_dgrad(const void* dY, const void* W, void* dX, int64_t rows_cap, int E, int OUT, int IN,
@@ -150,6 +154,36 @@ int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pr
         return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, (narrow_mask() & 1) != 0,
                          static_cast<cudaStream_t>(stream));
     return tc_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, static_cast<cudaStream_t>(stream));
+}
+
+static int check_peer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN, int32_t row_align) {
+    using namespace fmab;
+    FMAB_REQUIRE(dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "the peer-store GEMMs exist for bf16 only");
+    FMAB_REQUIRE(row_align > 0 && row_align % 256 == 0, FMA_B200_ERR_UNSUPPORTED,
+                 "the peer-store GEMMs run on CTA pairs: row_align=%d must be a multiple of 256", row_align);
+    return check_layer_gemm(dtype, rows_cap, E, OUT, IN);
+}
+
+int fma_b200_moe_gemm_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int32_t dtype,
+                                   int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN, const int32_t* mtile_expert,
+                                   int32_t row_align, void* stream) {
+    using namespace fmab;
+    if (int rc = check_peer_gemm(dtype, rows_cap, E, OUT, IN, row_align)) return rc;
+    if (rows_cap == 0) return FMA_B200_OK;
+    FMAB_REQUIRE(X && W && dst_table && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
+    FMAB_REQUIRE(aligned16(X) && aligned16(W), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
+    return tc2_forward_peer(X, W, dst_table, rows_cap, E, OUT, IN, mtile_expert, static_cast<cudaStream_t>(stream));
+}
+
+int fma_b200_moe_gemm_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int32_t dtype,
+                                 int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN, const int32_t* mtile_expert,
+                                 int32_t row_align, void* stream) {
+    using namespace fmab;
+    if (int rc = check_peer_gemm(dtype, rows_cap, E, OUT, IN, row_align)) return rc;
+    if (rows_cap == 0) return FMA_B200_OK;
+    FMAB_REQUIRE(dY && W && dst_table && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
+    FMAB_REQUIRE(aligned16(dY) && aligned16(W), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
+    return tc2_dgrad_peer(dY, W, dst_table, rows_cap, E, OUT, IN, mtile_expert, static_cast<cudaStream_t>(stream));
 }
 
 int64_t fma_b200_grouped_gemm_workspace_bytes(int32_t n_groups, int64_t total_mtiles) {

@@ -31,6 +31,7 @@ constexpr size_t GEMM_SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1
 constexpr int EPI_PLAIN = 0;
 constexpr int EPI_SWIGLU_FWD = 1;
 constexpr int EPI_SWIGLU_BWD = 2;
+constexpr int EPI_PLAIN_PEER = 3;  // CTA-pair kernel: plain epilogue whose 128-row tiles go to per-tile addresses
 
 constexpr int MODE_ROWS = 0;     // ragged M: m-tile -> expert through mtile_expert (forward, dgrad)
 constexpr int MODE_WGRAD = 1;    // ragged K: tile = (expert, m-tile, n-tile), k runs over the expert's rows
@@ -76,6 +77,7 @@ struct GemmParams {
     int32_t inter;                // SwiGLU: intermediate size I
     int32_t dynamic_tiles;        // 1: tiles drawn from the global counter; 0: tile = blockIdx.x + i * gridDim.x
     int32_t pair_skew;            // CTA-pair kernel: k-blocks by which accumulator half 1 trails half 0
+    const uint64_t* mtile_dst;    // EPI_PLAIN_PEER: byte address of output row 0 of every 128-row tile (pitch ldd)
 };
 
 // ---------------------------------------------------------------------------

@@ -52,6 +52,10 @@ struct PairShape {
     static constexpr int kStageBytes = A_STAGE_BYTES + HALVES * PAIR_B_BYTES;  // 16 KB + HALVES x 16 KB
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
 };
+// EPI_PLAIN_PEER stages every 32-row x 64-column piece of the output in shared memory (4 KB per epilogue
+// warp, behind the operand ring) so that it leaves the SM as whole 128-byte row segments.
+constexpr int PEER_PATCH_BYTES = 32 * 128;
+constexpr size_t PEER_PATCH_TOTAL = static_cast<size_t>(PAIR_EPI_WARPS) * PEER_PATCH_BYTES;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -515,6 +519,54 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     }
                     if (row_ok) store_row32_bf16(drow + c * 32, v, cols_left);
                 }
+            } else if (EPI == EPI_PLAIN_PEER) {
+                // The 128 rows of this CTA's tile go to one destination (possibly another GPU's memory):
+                // address of row 0 from the per-tile table, same pitch.  Stores that cross NVLink should be
+                // whole 128-byte lines, so two 32-column chunks are transposed through a 4 KB patch of shared
+                // memory: lane = row when the patch is written, (4 rows x 8 pieces of 16 B) per store
+                // instruction when it is read.  Pieces are XOR-swizzled by the row so that neither phase has
+                // bank conflicts.
+                uint8_t* dst_tile = reinterpret_cast<uint8_t*>(__ldg(p.mtile_dst + (t.d_row >> 7)));
+                const uint32_t patch = ring + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * PEER_PATCH_BYTES;
+                constexpr int kPairs = BN / 64 / 2;  // 64-column groups per warp and half
+#pragma unroll 1
+                for (int g = half * kPairs; g < (half + 1) * kPairs; ++g) {
+                    const int cols_left = n_valid - g * 64;
+                    if (cols_left <= 0) break;
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        float v[32];
+                        if (any_k && cols_left > q * 32) {
+                            tc_load_32(taddr + g * 64 + q * 32, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint4 w = Elem<__nv_bfloat16>::pack(v + k * 8);
+                            const uint32_t piece = static_cast<uint32_t>(q * 4 + k) ^ (lane & 7);
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 128 + piece * 16),
+                                         "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w)
+                                         : "memory");
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + (lane >> 3);   // row of the warp's 32
+                        const int piece = lane & 7;           // 16-byte piece of the 128-byte segment
+                        uint4 w;
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                                     : "r"(patch + r * 128 + ((piece ^ (r & 7)) * 16))
+                                     : "memory");
+                        const int row = quad * 32 + r;
+                        if (row < t.rows_valid && piece * 8 < cols_left)
+                            st_global_16(dst_tile + (static_cast<int64_t>(row) * p.ldd + n0h + g * 64 + piece * 8) * 2, w);
+                    }
+                    __syncwarp();
+                }
             } else if (EPI == EPI_SWIGLU_FWD) {
                 __nv_bfloat16* arow = p.d + grow * p.ldd + n0h;
                 __nv_bfloat16* prow = p.d2 ? p.d2 + grow * (2 * static_cast<int64_t>(p.inter)) + n0h : nullptr;
@@ -628,7 +680,7 @@ template <bool A_MN, bool B_MN, int EPI, int HALVES = 2>
 static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s) {
     static bool configured = false;
     auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI, HALVES>;
-    constexpr size_t PAIR_SMEM_BYTES = PairShape<HALVES>::kSmemBytes;
+    constexpr size_t PAIR_SMEM_BYTES = PairShape<HALVES>::kSmemBytes + (EPI == EPI_PLAIN_PEER ? PEER_PATCH_TOTAL : 0);
     if (!configured) {
         FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM_BYTES));
         configured = true;
@@ -725,6 +777,48 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     }
     if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD>(p, total, s);
     return launch_pair<false, true, EPI_PLAIN>(p, total, s);
+}
+
+// Forward / dgrad whose output tiles go to the addresses in dst_table (one per 128-row tile, row pitch = the
+// output width): the epilogue of the expert-parallel layer that returns rows straight into the arenas of the
+// ranks they came from.
+int tc2_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
+                     const int32_t* mtile_expert, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_pair_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, PAIR_B_ROWS)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.mtile_dst = dst_table;
+    p.ldd = OUT;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (OUT + 2 * BN - 1) / (2 * BN);
+    p.n_cols = OUT;
+    p.k_len = IN;
+    p.b_group_stride = OUT;
+    p.n_groups = E;
+    return launch_pair<false, false, EPI_PLAIN_PEER>(p, static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles, s);
+}
+
+int tc2_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
+                   const int32_t* mtile_expert, cudaStream_t s) {
+    GemmParams p;
+    if (int rc = fill_pair_common(p)) return rc;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK)) return rc;
+    p.mode = MODE_ROWS;
+    p.mtile_expert = mtile_expert;
+    p.mtile_dst = dst_table;
+    p.ldd = IN;
+    p.inter = IN;
+    p.n_mtiles = static_cast<int>(rows_cap / BM);
+    p.n_ntiles = (IN + 2 * BN - 1) / (2 * BN);
+    p.n_cols = IN;
+    p.k_len = OUT;
+    p.b_group_stride = OUT;
+    p.n_groups = E;
+    return launch_pair<false, true, EPI_PLAIN_PEER>(p, static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles, s);
 }
 
 int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,

@@ -199,3 +199,19 @@ def bias_grad(d_grouped: torch.Tensor, maps: RowMaps) -> torch.Tensor:
     call("fma_b200_moe_bias_grad", ptr(d_grouped), dtype_code(d_grouped.dtype), maps.num_experts, C,
          ptr(maps.pad_offsets), ptr(d_bias), stream_ptr(d_grouped.device))  # fmt: skip
     return d_bias
+
+
+def gemm_forward_peer(X: torch.Tensor, W: torch.Tensor, dst_table: torch.Tensor, mtile_expert: torch.Tensor,
+                      row_align: int = ROW_ALIGN) -> None:
+    """gemm_forward whose 128-row output tiles are stored at the byte addresses in dst_table (int64, one per tile)."""
+    E, OUT, IN = W.shape
+    call("fma_b200_moe_gemm_forward_peer", ptr(X), ptr(W), ptr(dst_table), dtype_code(X.dtype), X.size(0), E, OUT, IN,
+         ptr(mtile_expert), row_align, stream_ptr(X.device))  # fmt: skip
+
+
+def gemm_dgrad_peer(dY: torch.Tensor, W: torch.Tensor, dst_table: torch.Tensor, mtile_expert: torch.Tensor,
+                    row_align: int = ROW_ALIGN) -> None:
+    """gemm_dgrad whose 128-row output tiles are stored at the byte addresses in dst_table (int64, one per tile)."""
+    E, OUT, IN = W.shape
+    call("fma_b200_moe_gemm_dgrad_peer", ptr(dY), ptr(W), ptr(dst_table), dtype_code(dY.dtype), dY.size(0), E, OUT, IN,
+         ptr(mtile_expert), row_align, stream_ptr(dY.device))  # fmt: skip

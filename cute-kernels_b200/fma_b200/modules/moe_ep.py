@@ -311,6 +311,7 @@ class ExpertParallelMoE(MoE):
         overlap_chunks: int = 6,
         transport: str = "auto",
         capacity_factor: float = 1.5,
+        fuse_return: bool = False,
     ) -> None:
         if transport not in ("auto", "peer", "nccl"):
             raise ValueError(f"transport={transport!r}: expected 'auto', 'peer' or 'nccl'")
@@ -318,6 +319,8 @@ class ExpertParallelMoE(MoE):
         self.overlap_chunks = overlap_chunks
         self.transport = transport
         self.capacity_factor = capacity_factor
+        # peer transport only: the down projection / dgrad store their tiles straight into the senders' arenas
+        self.fuse_return = fuse_return
         self.last_transport = None  # "peer" or "nccl": what the most recent forward used
         self._arena = None
         self._peer_unavailable = None  # reason text once the peer transport has been given up
@@ -392,7 +395,7 @@ class ExpertParallelMoE(MoE):
         if arena.busy or max(plan.total_recv_rows) > arena.recv_cap:
             return None
         return P._EPPeerSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
-                                            arena, plan, gathered[:, :E].contiguous())  # fmt: skip
+                                            arena, plan, gathered[:, :E].contiguous(), self.fuse_return)  # fmt: skip
 
     def close_peer_transport(self) -> None:
         """Collective: frees the peer-memory arena (the next forward would create a new one)."""

@@ -120,10 +120,27 @@ class PeerPlan:
         return [(r, self.recv_base[r][c] + self.src_off[r][c][me], self.S[me][r * El + b[c]], self.rows[me][r][c])
                 for r in self.peer_order()]  # fmt: skip
 
+    def return_tiles(self, c: int) -> list[tuple[int, int]]:
+        """For every 128-row tile of chunk c in this rank's receive layout: (rank it came from, first row of
+        the tile in that rank's grouped layout) - where a fused GEMM epilogue has to store the tile."""
+        me, El = self.rank, self.num_local_experts
+        e0, e1 = self.experts(c)
+        out = []
+        for s in range(self.world_size):
+            for e in range(me * El + e0, me * El + e1):
+                first = self.S[s][e]
+                out += [(s, first + 128 * j) for j in range((self.S[s][e + 1] - first) // 128)]
+        return out
+
     def return_copies(self, c: int) -> list[tuple[int, int, int, int]]:
         """Rows of my chunk-local result (receive order) -> the grouped layout of the rank they came from."""
         me, El, b = self.rank, self.num_local_experts, self.bounds
         return [(s, self.S[s][me * El + b[c]], self.src_off[me][c][s], self.rows[s][me][c]) for s in self.peer_order()]
+
+
+def _upload(array, device: torch.device) -> torch.Tensor:
+    """Host array -> device tensor through pinned memory, asynchronously on the current stream."""
+    return torch.from_numpy(array).pin_memory().to(device, non_blocking=True)
 
 
 class _RawCudaMemory:
@@ -287,6 +304,24 @@ class PeerArena:
         nbytes = (ctypes.c_int64 * n)(*[k * rb for _, _, _, k in copies])
         _native.call("fma_b200_peer_copy", n, dst, srcs, nbytes, _native.stream_ptr(self.device))
 
+    def return_tables(self, plan: PeerPlan) -> tuple[torch.Tensor, list[int]]:
+        """Destination addresses for the GEMMs that store into the senders' arenas: an int64 device tensor
+        [2, tiles] (row 0: into `back`, row 1: into `d_xg`) over all chunks, and the first tile of every chunk."""
+        import numpy as np
+
+        tiles, first = [], [0]
+        for c in range(plan.n_chunks):
+            tiles += plan.return_tiles(c)
+            first.append(len(tiles))
+        n = max(len(tiles), 1)
+        table = np.zeros((2, n), dtype=np.int64)
+        if tiles:
+            base = np.array([self.peer_ptrs[s] for s, _ in tiles], dtype=np.int64)
+            rows = np.array([row for _, row in tiles], dtype=np.int64)
+            table[0, : len(tiles)] = base + self.region_off["back"] + rows * self.row_bytes
+            table[1, : len(tiles)] = base + self.region_off["d_xg"] + rows * self.row_bytes
+        return _upload(table, self.device), first
+
     def signal(self, kind: int, chunk: int, seq: int) -> None:
         n = self.world_size
         idx = 4 * self._flag_index(kind, chunk, self.rank)
@@ -304,7 +339,8 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
     pipelined over chunks of local experts; the backward mirrors it."""
 
     @staticmethod
-    def forward(ctx, x, weights, w_fc, w_proj, maps: K.RowMaps, arena: PeerArena, plan: PeerPlan, counts_dev):
+    def forward(ctx, x, weights, w_fc, w_proj, maps: K.RowMaps, arena: PeerArena, plan: PeerPlan, counts_dev,
+                fuse_return: bool = False):
         x, weights, w_fc, w_proj = x.contiguous(), weights.contiguous(), w_fc.contiguous(), w_proj.contiguous()
         T = x.size(0)
         dev = x.device
@@ -313,6 +349,9 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         arena.seq += 1
         seq = arena.seq
 
+        # fuse_return: the down projection (and, in the backward pass, the dgrad) stores its tiles straight
+        # into the arenas of the ranks the rows came from, so no result buffer and no return copies exist
+        tables, first_tile = arena.return_tables(plan) if fuse_return else (None, None)
         xg = K.scatter(x, maps)
         ready = torch.cuda.Event()
         ready.record(main)
@@ -340,14 +379,18 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
                    K.stream_ptr(dev))  # fmt: skip
             arena.wait(FLAG_FWD_DISPATCH, c, seq)
             pre, act = K.gemm_forward_swiglu(rows, w_fc[e0:e1], mt, keep_pre=True)
-            out = K.gemm_forward(act, w_proj[e0:e1], mt)
-            done = torch.cuda.Event()
-            done.record(main)
-            out.record_stream(comm)
-            with torch.cuda.stream(comm):
-                comm.wait_event(done)
-                arena.push(plan.return_copies(c), out, "back")
-                arena.signal(FLAG_FWD_RETURN, c, seq)
+            if fuse_return:
+                K.gemm_forward_peer(act, w_proj[e0:e1], tables[0, first_tile[c] :], mt)
+                arena.signal(FLAG_FWD_RETURN, c, seq)  # after the GEMM, in stream order
+            else:
+                out = K.gemm_forward(act, w_proj[e0:e1], mt)
+                done = torch.cuda.Event()
+                done.record(main)
+                out.record_stream(comm)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    arena.push(plan.return_copies(c), out, "back")
+                    arena.signal(FLAG_FWD_RETURN, c, seq)
             if c + 2 < C:
                 dispatch(c + 2)
             recv.append(rows)
@@ -364,6 +407,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
             ctx.lease = arena.lease()
         ctx.save_for_backward(back, weights, w_fc, w_proj, *recv, *pres, *acts, *seg_offs, *mtiles)
         ctx.maps, ctx.T, ctx.plan, ctx.arena, ctx.seq = maps, T, plan, arena, seq
+        ctx.tables, ctx.first_tile = tables, first_tile
         return y
 
     @staticmethod
@@ -406,14 +450,18 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
             d_pre = K.gemm_dgrad_swiglu(d_out, w_proj[e0:e1], pres[c], mtiles[c])
             if need_fc:
                 K.gemm_wgrad(d_pre, recv[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_fc[e0:e1])
-            d_recv = K.gemm_dgrad(d_pre, w_fc[e0:e1], mtiles[c])
-            done = torch.cuda.Event()
-            done.record(main)
-            d_recv.record_stream(comm)
-            with torch.cuda.stream(comm):
-                comm.wait_event(done)
-                arena.push(plan.return_copies(c), d_recv, "d_xg")
+            if ctx.tables is not None:
+                K.gemm_dgrad_peer(d_pre, w_fc[e0:e1], ctx.tables[1, ctx.first_tile[c] :], mtiles[c])
                 arena.signal(FLAG_BWD_RETURN, c, seq)
+            else:
+                d_recv = K.gemm_dgrad(d_pre, w_fc[e0:e1], mtiles[c])
+                done = torch.cuda.Event()
+                done.record(main)
+                d_recv.record_stream(comm)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    arena.push(plan.return_copies(c), d_recv, "d_xg")
+                    arena.signal(FLAG_BWD_RETURN, c, seq)
             if c + 2 < C:
                 dispatch(c + 2)
         # every rank waits for all returns even if it needs no input gradient: the peers' pushes into
@@ -422,4 +470,4 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
             arena.wait(FLAG_BWD_RETURN, c, seq)
         d_x = K.scatter_backward(arena.regions["d_xg"][: maps.rows_cap], maps, ctx.T) if need_x else None
         ctx.lease = None
-        return d_x, d_w, d_w_fc, d_w_proj, None, None, None, None
+        return d_x, d_w, d_w_fc, d_w_proj, None, None, None, None, None

@@ -343,6 +343,21 @@ int fma_b200_grouped_gemm(const void* A, const void* B, void* D, const uint32_t*
  * peer_wait           one small kernel: returns when flags[i] - value >= 0 for all i < n, or records
  *                     device status 0x7002 after timeout_ms (1..60000) and returns.
  */
+/*
+ * moe_gemm_forward_peer / moe_gemm_dgrad_peer: fma_b200_moe_gemm_forward / _dgrad (bf16, row_align a multiple
+ * of 256) whose output is not one matrix: the 128 rows of m-tile i are stored at byte address dst_table[i]
+ * (device array, rows_cap/128 entries; row pitch OUT resp. IN elements; addresses 16-byte aligned), which may
+ * lie in a buffer opened with peer_buffer_open.  The expert-parallel layer uses them to return expert
+ * outputs and input gradients straight into the arenas of the ranks the rows came from.  Entries of tiles
+ * beyond the used rows (mtile_expert < 0) are not read.
+ */
+int fma_b200_moe_gemm_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int32_t dtype,
+                                   int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN, const int32_t* mtile_expert,
+                                   int32_t row_align, void* stream);
+int fma_b200_moe_gemm_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int32_t dtype,
+                                 int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN, const int32_t* mtile_expert,
+                                 int32_t row_align, void* stream);
+
 #define FMA_B200_PEER_HANDLE_BYTES 64
 int fma_b200_peer_buffer_create(int64_t bytes, void** ptr_out, uint8_t* handle_out);
 int fma_b200_peer_buffer_open(const uint8_t* handle, void** ptr_out);

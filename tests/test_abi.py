@@ -58,6 +58,10 @@ def test_status_strings_and_bad_arguments_without_gpu():
     assert lib.fma_b200_moe_bias_add(null, null, 1, 128, 12, null, null, null) == 1  # width not 16-byte multiple
     assert lib.fma_b200_moe_bias_add(null, null, 1, 0, 64, null, null, null) == 0  # nothing to do
     assert lib.fma_b200_moe_bias_grad(null, 1, 0, 64, null, null, null) == 1  # E < 1
+    assert lib.fma_b200_moe_gemm_forward_peer(null, null, null, 0, 256, 2, 64, 64, null, 256, null) == 2  # f32
+    assert lib.fma_b200_moe_gemm_forward_peer(null, null, null, 1, 256, 2, 64, 64, null, 128, null) == 2  # row_align
+    assert lib.fma_b200_moe_gemm_dgrad_peer(null, null, null, 1, 256, 2, 64, 64, null, 256, null) == 1  # NULL pointers
+    assert lib.fma_b200_moe_gemm_dgrad_peer(null, null, null, 1, 0, 2, 64, 64, null, 256, null) == 0  # no rows
     assert lib.fma_b200_peer_buffer_create(0, null, null) == 1
     assert lib.fma_b200_peer_buffer_open(null, null) == 1
     assert lib.fma_b200_peer_copy(0, null, null, null, null) == 0

@@ -118,6 +118,24 @@ class FakeArena:
         self.regions = {name: FakeTensor.make(cap, ready=True) for name, cap in caps.items()}
         self.row_seq = {name: np.zeros(cap, dtype=np.int64) for name, cap in caps.items()}
         self.flags = np.zeros((4, 16, sim.world), dtype=np.int64)
+        # made-up address space for the fused-return tables: rank r's arena starts at (r + 1) << 40
+        self.device = torch.device("cpu")
+        self.row_bytes = 2 * H
+        self.peer_ptrs = [(r + 1) << 40 for r in range(sim.world)]
+        self.region_off = {name: (i + 1) << 32 for i, name in enumerate(caps)}
+
+    def return_tables(self, plan):
+        from fma_b200.modules.moe_ep_peer import PeerArena
+
+        return PeerArena.return_tables(self, plan)
+
+    def mark_tiles(self, table, n_tiles, seq):
+        """What a GEMM with per-tile destinations does: 128 rows at every address of the table."""
+        for addr in table[:n_tiles].tolist():
+            peer, rest = (addr >> 40) - 1, addr & ((1 << 40) - 1)
+            region = {off: name for name, off in self.region_off.items()}[rest >> 32 << 32]
+            row = (rest & ((1 << 32) - 1)) // self.row_bytes
+            self.arenas[peer].row_seq[region][row : row + 128] = seq
 
     def lease(self):
         return object()
@@ -221,6 +239,19 @@ def _install(monkeypatch, sim: Sim, arenas: list, plans: list):
     monkeypatch.setattr(K, "gemm_forward_swiglu", gemm_forward_swiglu)
     monkeypatch.setattr(K, "gemm_forward", lambda X, W, mt, row_align=256: kernel(X.size(0), "down projection", **reads_of(X)))
     monkeypatch.setattr(K, "gemm_dgrad", lambda dY, W, mt, row_align=256: kernel(dY.size(0), "dgrad", **reads_of(dY)))
+    monkeypatch.setattr(P, "_upload", lambda array, device: torch.from_numpy(array))
+
+    def gemm_to_peers(what):
+        def fn(X, W, table, mt, row_align=256):
+            arena, seq, n_tiles = arenas[sim.rank], arenas[sim.rank].seq, X.size(0) // 128
+            out = kernel(1, what, **reads_of(X))
+            sim.enqueue(lambda: True, lambda: arena.mark_tiles(table, n_tiles, seq), what + " stores")
+            return out
+
+        return fn
+
+    monkeypatch.setattr(K, "gemm_forward_peer", gemm_to_peers("down projection into the senders' arenas"))
+    monkeypatch.setattr(K, "gemm_dgrad_peer", gemm_to_peers("dgrad into the senders' arenas"))
     monkeypatch.setattr(K, "gemm_dgrad_swiglu",
                         lambda d_out, W, pre, mt, row_align=256: kernel(d_out.size(0), "dgrad+swiglu", **reads_of(d_out, pre)))
     monkeypatch.setattr(K, "gemm_wgrad",
@@ -252,9 +283,10 @@ class FakeCtx:
         self.saved_tensors = tensors
 
 
+@pytest.mark.parametrize("fuse_return", [False, True])
 @pytest.mark.parametrize("train", [True, False])
 @pytest.mark.parametrize("world,experts,chunks,seed", [(2, 8, 3, 0), (4, 32, 6, 1), (8, 128, 6, 2), (8, 64, 8, 3), (3, 12, 1, 4)])
-def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts, chunks, seed, train):
+def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts, chunks, seed, train, fuse_return):
     from fma_b200.modules.moe_ep_peer import PeerPlan
 
     rng = np.random.default_rng(seed)
@@ -304,7 +336,7 @@ def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts,
             x = torch.zeros(5, H)
             P._EPPeerSwigluExperts.forward(ctxs[r], x, torch.zeros(5, 2), torch.zeros(experts // world, 2, H),
                                            torch.zeros(experts // world, H, 1), maps_for(r, counts), arenas[r], plans[r],
-                                           torch.zeros(world, experts, dtype=torch.int32))  # fmt: skip
+                                           torch.zeros(world, experts, dtype=torch.int32), fuse_return)  # fmt: skip
         if step % 2 == 0:  # sometimes the host is far ahead of the device, sometimes not
             sim.run(until=lambda: sim.rng.random() < 0.02 or sim.idle())
         if not train:  # forward-only calls back to back (evaluation): the arena is reused at once
