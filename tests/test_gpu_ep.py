@@ -54,9 +54,11 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
 
         shard = fma_b200.shard_expert_state_dict(full.state_dict(), rank, world)
         results = {}
-        for transport in ("peer", "nccl"):
+        for case in ("peer", "nccl", "peer fused"):
+            # "peer fused": the down projection and the dgrad store their tiles straight into the senders' arenas
+            transport = case.split()[0]
             ep = fma_b200.ExpertParallelMoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02, overlap_chunks=3,
-                                            transport=transport)  # fmt: skip
+                                            transport=transport, fuse_return=case.endswith("fused"))  # fmt: skip
             ep = ep.to(dev).to(dtype)
             ep.load_state_dict(shard, strict=True)
             for step in range(3):  # the arena is reused from the second step on
@@ -75,11 +77,11 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
                     "d_w_fc": _rel(ep.c_fc.weight.grad, full.c_fc.weight.grad[e0:e1]),
                     "d_w_proj": _rel(ep.c_proj.weight.grad, full.c_proj.weight.grad[e0:e1]),
                 }
-                assert all(v <= 1e-2 for v in errs.values()), (transport, step, errs)
+                assert all(v <= 1e-2 for v in errs.values()), (case, step, errs)
                 # y is a per-token computation: the expert-parallel result matches the local one bit for bit
                 assert torch.equal(y, y_all[lo:hi])
-            results[transport] = (y, x.grad, ep.c_fc.weight.grad.clone(), ep.c_proj.weight.grad.clone())
-            if transport == "peer":
+            results[case] = (y, x.grad, ep.c_fc.weight.grad.clone(), ep.c_proj.weight.grad.clone())
+            if case == "peer":
                 # a second forward while the first one's backward is pending must not touch the arena
                 x1 = xs[rank].clone().requires_grad_(True)
                 y1, _ = ep(x1)
@@ -95,9 +97,12 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
                     y3, _ = ep(xs[rank])
                 assert ep.last_transport == "peer" and torch.equal(y3, y_all[lo:hi])
                 ep.close_peer_transport()
-        # both transports move the same rows into the same layouts: identical results
-        for a, b in zip(results["peer"], results["nccl"]):
-            assert torch.equal(a, b)
+            elif case == "peer fused":
+                ep.close_peer_transport()
+        # every variant moves the same rows into the same layouts: identical results
+        for case in ("peer", "peer fused"):
+            for a, b in zip(results[case], results["nccl"]):
+                assert torch.equal(a, b), case
         from fma_b200 import _native
 
         assert _native.device_status() == 0
