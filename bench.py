@@ -225,54 +225,71 @@ def algorithmic_work(cfg: dict) -> dict:
 # ---------------------------------------------------------------------------------------------
 # CPU baseline (the oracle port), bounded sample
 # ---------------------------------------------------------------------------------------------
-def cpu_sample_tokens(cfg: dict) -> int:
-    """Tokens of the bounded CPU sample: about 0.25 TFLOP of expert GEMMs (10-20 s on a 16-thread host),
-    at least one row per expert on average, never more than the workload itself."""
-    per_token = 18 * cfg["k"] * cfg["H"] * cfg["I"]
-    t = int(0.25e12 / per_token)
-    t = max(t, cfg["E"] // cfg["k"], 64)
-    return min(t, cfg["T"])
+CPU_SAMPLE_FLOPS = 0.6e12  # expert-GEMM work of one CPU pass (forward + backward)
 
 
-def cpu_oracle_pass(cfg: dict, weights: dict, seed: int) -> tuple[float, int]:
-    """One forward+backward of the oracle on a seeded sample; returns (seconds, tokens)."""
+def cpu_sample(cfg: dict) -> tuple[int, int]:
+    """(experts, tokens) of the bounded CPU sample.  The sample keeps what decides the cost per token: the
+    per-expert problem.  It takes k of the E experts and routes every sampled token to all k of them, so each
+    expert sees as many rows as tokens are sampled; the token count is what the full workload gives an expert
+    (T*k/E rows under uniform routing), capped so that one pass stays near CPU_SAMPLE_FLOPS.  (A sample of few
+    tokens over ALL experts would time weight-sized work - reading and rounding every expert's weights and
+    weight gradients - that the full workload amortises over thousands of rows per expert.)"""
+    if 18 * cfg["T"] * cfg["k"] * cfg["H"] * cfg["I"] <= CPU_SAMPLE_FLOPS:
+        return cfg["E"], cfg["T"]  # the whole workload is small enough: all experts, real top-k routing
+    e_s = min(cfg["E"], cfg["k"])
+    full_load = max(1, cfg["T"] * cfg["k"] // cfg["E"])
+    budget = int(CPU_SAMPLE_FLOPS / (18 * cfg["k"] * cfg["H"] * cfg["I"]))
+    return e_s, max(64, min(full_load, budget, cfg["T"]))
+
+
+def cpu_oracle_pass(cfg: dict, weights: dict, seed: int, tokens: int = 0) -> tuple[float, int]:
+    """One forward+backward of the oracle on a seeded sample; returns (seconds, tokens).  `weights` holds the
+    sampled experts (cpu_sample(cfg)[0] of them); `tokens` overrides the sample's token count (warm-up)."""
     from oracle import moe_oracle as O
 
-    t_s = cpu_sample_tokens(cfg)
+    e_s = weights["w_fc"].shape[0]
+    t_s = tokens or cpu_sample(cfg)[1]
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((t_s, cfg["H"]), dtype=np.float32)
     dy = rng.standard_normal((t_s, cfg["H"]), dtype=np.float32)
     if cfg["dtype"] == "bf16":
         x, dy = O.bf16_round(x), O.bf16_round(dy)
     t0 = time.perf_counter()
-    fwd = O.moe_forward(x, weights["w_gate"], weights["w_fc"], weights["w_proj"], cfg["k"], cfg["dtype"],
-                        gate_bias=weights.get("gate_bias"))
+    fwd = O.moe_forward(x, weights["w_gate"][:e_s], weights["w_fc"][:e_s], weights["w_proj"][:e_s], min(cfg["k"], e_s),
+                        cfg["dtype"])  # fmt: skip
     O.moe_backward(fwd, dy, keep_weight_grads=False)
     return time.perf_counter() - t0, t_s
 
 
-def host_weights_from_layer(layer) -> dict:
+def cpu_sample_text(cfg: dict) -> str:
+    e_s, t_s = cpu_sample(cfg)
+    if e_s == cfg["E"]:
+        return (f"the whole workload ({t_s} tokens, top-{cfg['k']} of {e_s} experts), numpy fp32 matmul with "
+                f"{cfg['dtype']} rounding points")
+    return (f"{t_s} tokens, each routed to the same {e_s} of the {cfg['E']} experts ({t_s} rows per expert; the full "
+            f"workload gives an expert {cfg['T'] * cfg['k'] // cfg['E']}), numpy fp32 matmul with {cfg['dtype']} "
+            f"rounding points")
+
+
+def host_weights_from_layer(layer, n_experts: int) -> dict:
+    """The router weight and the first n_experts experts of the layer, as float32 host arrays."""
     f = lambda t: t.detach().float().cpu().numpy()  # noqa: E731
-    w = {"w_gate": f(layer.gate.weight), "w_fc": f(layer.c_fc.weight), "w_proj": f(layer.c_proj.weight)}
-    if getattr(layer.gate, "bias", None) is not None:
-        w["gate_bias"] = f(layer.gate.bias)
-    return w
+    return {"w_gate": f(layer.gate.weight[:n_experts]), "w_fc": f(layer.c_fc.weight[:n_experts]),
+            "w_proj": f(layer.c_proj.weight[:n_experts])}  # fmt: skip
 
 
 def host_weights_seeded(cfg: dict) -> dict:
-    """Weights for the reference arm when no GPU copy exists: seeded N(0, 0.02), bf16-rounded if needed."""
+    """Weights of the sampled experts for the reference arm: seeded N(0, 0.02), bf16-rounded if needed."""
     from oracle import moe_oracle as O
 
     rng = np.random.default_rng(1000)
-    E, H, I = cfg["E"], cfg["H"], cfg["I"]
+    E, H, I = cpu_sample(cfg)[0], cfg["H"], cfg["I"]
     w = {"w_gate": rng.standard_normal((E, H), dtype=np.float32) * 0.02,
          "w_fc": rng.standard_normal((E, 2 * I, H), dtype=np.float32) * 0.02,
          "w_proj": rng.standard_normal((E, H, I), dtype=np.float32) * 0.02}  # fmt: skip
     if cfg["dtype"] == "bf16":
         w = {n: O.bf16_round(a) for n, a in w.items()}
-    if cfg["router"] == "zipf":
-        p = 1.0 / np.arange(1, E + 1)
-        w["gate_bias"] = np.log(p / p.sum())[np.random.default_rng(3).permutation(E)].astype(np.float32)
     return w
 
 
@@ -311,8 +328,7 @@ def run_reference(args, cfg: dict, name: str) -> None:
         "config": {"workload": name, **{k: cfg[k] for k in ("T", "H", "E", "k", "I")},
                    "note": "CPU port of the reference torch backend; each step is a bounded sample of the workload"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
-                         "sample": f"{toks // args.steps} tokens per step, all {cfg['E']} experts, numpy fp32 matmul "
-                                   f"with {cfg['dtype']} rounding points"},
+                         "sample": "per step: " + cpu_sample_text(cfg)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }  # fmt: skip
@@ -642,12 +658,11 @@ def main() -> None:
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        weights = host_weights_from_layer(layer)
-        cpu_oracle_pass({**cfg, "T": min(cfg["T"], 64)}, weights, seed=0)  # warm the BLAS threads
+        weights = host_weights_from_layer(layer, cpu_sample(cfg)[0])
+        cpu_oracle_pass(cfg, weights, seed=0, tokens=64)  # warm the BLAS threads
         secs, toks = cpu_oracle_pass(cfg, weights, seed=1)
         cpu_baseline = {"value": toks / secs, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
-                        "sample": f"one forward+backward of {toks} tokens over all {cfg['E']} experts "
-                                  f"({secs:.1f} s), numpy with {cfg['dtype']} rounding points"}  # fmt: skip
+                        "sample": f"one forward+backward ({secs:.1f} s) of " + cpu_sample_text(cfg)}  # fmt: skip
 
     line = {
         "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,

@@ -39,9 +39,12 @@ def test_algorithmic_work_per_step():
 def test_cpu_sample_is_bounded():
     bench = _bench()
     for cfg in bench.WORKLOADS.values():
-        toks = bench.cpu_sample_tokens(cfg)
-        assert 1 <= toks <= cfg["T"]
-        assert 18 * cfg["k"] * cfg["H"] * cfg["I"] * toks <= 0.3e12 or toks == max(cfg["E"] // cfg["k"], 64)
+        experts, toks = bench.cpu_sample(cfg)
+        assert 1 <= toks <= cfg["T"] and 1 <= experts <= cfg["E"]
+        assert experts == cfg["E"] or experts == cfg["k"]  # the whole workload, or k experts that every token visits
+        assert 18 * cfg["k"] * cfg["H"] * cfg["I"] * toks <= bench.CPU_SAMPLE_FLOPS or toks == 64
+        assert toks <= max(64, cfg["T"] * cfg["k"] // cfg["E"]) or experts == cfg["E"]  # never more rows per expert than the workload gives
+        assert bench.cpu_sample_text(cfg)
 
 
 def test_reference_arm_json_line():
