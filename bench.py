@@ -420,7 +420,7 @@ def main() -> None:
     ap.add_argument("--ep-chunks", type=int, default=6, help="expert chunks whose exchanges overlap the GEMMs (N > 1)")
     ap.add_argument("--ep-transport", choices=["auto", "peer", "nccl"], default="auto",
                     help="row exchange of the expert-parallel layer: copy-engine pushes into peer-mapped arenas, "
-                         "or NCCL all-to-all; auto = peer when the arenas can be mapped (N > 1)")
+                         "or NCCL all-to-all; auto = peer on 2 GPUs (if the arenas can be mapped), NCCL above (N > 1)")
     ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for the all-to-all kernels (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
