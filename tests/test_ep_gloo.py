@@ -158,3 +158,20 @@ def test_peer_plan_routes_every_block(world, E, chunks, align):
                 back[s][dst : dst + n] = out[src : src + n]
     for s in range(world):
         np.testing.assert_array_equal(back[s], xg[s])
+
+
+def test_chunk_bounds_cover_all_experts():
+    """Pipeline chunks: strictly increasing bounds from 0 to the expert count, never more chunks than
+    experts, small first and last chunk once there are at least 4 chunks and 8 experts."""
+    sys.path.insert(0, str(ROOT / "cute-kernels_b200"))
+    from fma_b200.modules.moe_ep import chunk_bounds
+
+    for experts in (1, 2, 3, 7, 8, 16, 32, 64, 128):
+        for chunks in (1, 2, 3, 4, 6, 8, 16, 200):
+            b = chunk_bounds(experts, chunks)
+            assert b[0] == 0 and b[-1] == experts and all(x < y for x, y in zip(b, b[1:]))
+            assert len(b) - 1 <= min(chunks, experts)
+            if chunks >= 4 and experts >= 8:
+                sizes = [y - x for x, y in zip(b, b[1:])]
+                assert sizes[0] == sizes[-1] == max(1, experts // 16)
+                assert max(sizes[1:-1]) - min(sizes[1:-1]) <= 1
