@@ -25,6 +25,7 @@ Backward runs the same two exchanges in reverse.
 
 from __future__ import annotations
 
+import os
 from typing import Callable
 
 import torch
@@ -35,7 +36,7 @@ from .moe import MoE, _is_swiglu_packed
 
 ROW_ALIGN = K.ROW_ALIGN
 # transport="auto" uses the peer-memory transport up to this group size and NCCL all-to-all above it.
-PEER_AUTO_MAX_RANKS = 2
+PEER_AUTO_MAX_RANKS = int(os.environ.get("FMA_B200_PEER_AUTO_MAX_RANKS", "2"))
 
 
 def exchange_counts(expert_count: torch.Tensor, world_size: int, group) -> torch.Tensor:
