@@ -23,6 +23,7 @@ import torch.nn as nn
 
 from .. import _native
 from ..kernel_backend import KernelBackend
+from ..ops.grouped_gemm import grouped_gemm
 from ..ops.swiglu import swiglu_packed
 from . import _kernels as K
 
@@ -137,6 +138,42 @@ class _FusedSwigluExperts(torch.autograd.Function):
         return d_x, d_w, d_w_fc, d_w_proj, None
 
 
+class _GroupedGemmExperts(torch.autograd.Function):
+    """The reference's expert linear on its own layout (fma/modules/moe/cuda_implementation/__init__.py:15-80):
+    x holds the rows of expert e in M_array[e] consecutive rows (no alignment requirement), weight is
+    [E, N, K]; forward and both gradients are calls of the general grouped GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, weight, M_array, N_array, K_array):
+        x, weight = x.contiguous(), weight.contiguous()
+        _, N, K = weight.size()
+        assert N % 8 == 0 and K % 8 == 0
+        output = grouped_gemm(A=x, B=weight, C=None, M_array=M_array, N_array=N_array, K_array=K_array,
+                              output_shape=(x.size(0), N), is_A_transposed=False, is_B_transposed=True)  # fmt: skip
+        ctx.save_for_backward(x, weight, M_array, K_array, N_array)
+        return output
+
+    @staticmethod
+    def backward(ctx, output_grad):
+        x, weight, M_array, K_array, N_array = ctx.saved_tensors
+        output_grad = output_grad.contiguous()
+        x_grad = weight_grad = None
+        if ctx.needs_input_grad[0]:
+            x_grad = grouped_gemm(A=output_grad, B=weight, C=None, M_array=M_array, N_array=K_array, K_array=N_array,
+                                  output_shape=x.size(), is_A_transposed=False, is_B_transposed=False)  # fmt: skip
+        if ctx.needs_input_grad[1]:
+            weight_grad = grouped_gemm(A=output_grad, B=x, C=None, M_array=N_array, N_array=K_array, K_array=M_array,
+                                       output_shape=weight.size(), is_A_transposed=True, is_B_transposed=False)  # fmt: skip
+        return x_grad, weight_grad, None, None, None
+
+
+def grouped_gemm_experts(x: torch.Tensor, weight: torch.Tensor, M_array: torch.Tensor, N_array: torch.Tensor,
+                         K_array: torch.Tensor) -> torch.Tensor:
+    """y[rows of expert e] = x[rows of expert e] @ weight[e].T with the reference's signature
+    (fma/modules/moe/cuda_implementation/__init__.py: grouped_gemm_experts); bf16, differentiable in x and weight."""
+    return _GroupedGemmExperts.apply(x, weight, M_array, N_array, K_array)
+
+
 def _is_swiglu_packed(fn: Callable) -> bool:
     """True if `fn` is this package's swiglu_packed (possibly wrapped in functools.partial with
     backend keywords only), so that it can run inside the GEMM epilogue."""
@@ -169,6 +206,12 @@ class Experts(nn.Module):
         self.register_buffer("K_array", torch.empty((num_experts,), dtype=torch.uint32))
 
         self.reset_parameters()
+
+    def cuda_forward(self, input: torch.Tensor, expert_frequency: torch.Tensor) -> torch.Tensor:
+        """The reference's entry point (fma/modules/moe/__init__.py:89-92): `input` holds expert_frequency[e]
+        consecutive rows for expert e.  Like the reference it applies no bias."""
+        return grouped_gemm_experts(x=input, weight=self.weight, M_array=expert_frequency, N_array=self.N_array,
+                                    K_array=self.K_array)  # fmt: skip
 
     def grouped_forward(self, input: torch.Tensor, maps: K.RowMaps) -> torch.Tensor:
         """Y = X . W[e]^T over the grouped layout (rows of expert e in maps.pad_offsets[e:e+2])."""
