@@ -86,7 +86,8 @@ def run_layer(fma, T, H, E, k, I, dtype, seed, add_bias=False):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds fma/)")
-    ap.add_argument("--only-bias", action="store_true", help="write only the add_bias=True layer fixtures")
+    ap.add_argument("--only-bias", action="store_true",
+                    help="write only the fixtures added after the first set (add_bias=True layers, the float16 layer)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -105,6 +106,11 @@ def main() -> None:
         meta = {k: (str(v) if isinstance(v, torch.dtype) else v) for k, v in cfg.items()}
         np.savez_compressed(HERE / f"{name}.npz", meta=json.dumps(meta), **out)
         print(name, {k: v.shape for k, v in out.items() if k in ("y", "dx", "d_b_fc")})
+    # ---- layer in float16 (the reference's ops are dtype-generic; the kernels of this repository are not yet) ----
+    out, _ = run_layer(fma, T=96, H=64, E=8, k=2, I=32, dtype=torch.float16, seed=17)
+    cfg16 = dict(T=96, H=64, E=8, k=2, I=32, dtype=str(torch.float16), seed=17)
+    np.savez_compressed(HERE / "layer_f16_small.npz", meta=json.dumps(cfg16), **out)
+    print("layer_f16_small", out["y"].shape)
     if args.only_bias:
         return
 

@@ -72,6 +72,19 @@ def test_layer_with_expert_bias_matches_reference(golden_dir, name):
         assert O.rel_l2(bwd[key], z[key]) < tol, key
 
 
+def test_layer_float16_matches_reference(golden_dir):
+    """The oracle with IEEE-half rounding points against the reference run in float16 (the dtype the kernels
+    of this repository do not cover yet: this pins the checker for it)."""
+    z, meta = _load(golden_dir, "layer_f16_small")
+    fwd = O.moe_forward(z["x"], z["w_gate"], z["w_fc"], z["w_proj"], meta["k"], "f16", logits=z["router_logits"])
+    assert np.array_equal(np.sort(fwd["selected"], -1), np.sort(z["selected"], -1))
+    np.testing.assert_array_equal(fwd["expert_count"], z["expert_count"])
+    bwd = O.moe_backward(fwd, z["g"])
+    assert O.rel_l2(fwd["y"], z["y"]) < 1e-3
+    for key in ("dx", "d_w_fc", "d_w_proj"):
+        assert O.rel_l2(bwd[key], z[key]) < 1e-3, key
+
+
 def test_layer_config1_statistics(golden_dir):
     """The small fp32 configuration (T=4096, H=1024, E=8, top-2, I=512, seed 0) regenerated from its
     recipe and compared with the statistics the reference produced."""
