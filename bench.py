@@ -293,16 +293,23 @@ def host_weights_seeded(cfg: dict) -> dict:
     return w
 
 
-def cpu_threads() -> int:
-    try:
-        from threadpoolctl import threadpool_info
+CPU_THREADS_MAX = 16
 
+
+def pin_cpu_threads() -> int:
+    """Sets the BLAS thread count of the CPU arm itself - min(host cores, 16) - so that it does not depend on
+    what the launcher exported (torchrun sets OMP_NUM_THREADS=1); returns the count in effect."""
+    want = max(1, min(os.cpu_count() or 1, CPU_THREADS_MAX))
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+
+        threadpool_limits(limits=want, user_api="blas")
         n = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
         if n:
             return int(max(n))
     except Exception:
         pass
-    return os.cpu_count() or 1
+    return 1
 
 
 # ---------------------------------------------------------------------------------------------
@@ -312,6 +319,7 @@ def run_reference(args, cfg: dict, name: str) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    threads = pin_cpu_threads()
     weights = host_weights_seeded(cfg)
     for i in range(args.warmup):
         cpu_oracle_pass(cfg, weights, seed=i)
@@ -327,7 +335,7 @@ def run_reference(args, cfg: dict, name: str) -> None:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
         "config": {"workload": name, **{k: cfg[k] for k in ("T", "H", "E", "k", "I")},
                    "note": "CPU port of the reference torch backend; each step is a bounded sample of the workload"},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "per step: " + cpu_sample_text(cfg)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -338,9 +346,10 @@ def run_reference(args, cfg: dict, name: str) -> None:
 # ---------------------------------------------------------------------------------------------
 # continuous_count workload
 # ---------------------------------------------------------------------------------------------
-def run_count(args, peaks, peaks_kind) -> None:
+def measure_count(peaks: dict, steps: int, warmup: int, variants=(0,), big: bool = True) -> tuple[dict, float]:
+    """continuous_count on 2^24 int32 ids in 128 bins, uniform and Zipf(1.1): {case: ms, GB/s, fraction of the
+    HBM peak} and the CPU time of torch.bincount on the same ids (ms)."""
     import fma_b200
-    from fma_b200 import _native
 
     dev = torch.device("cuda:0")
     n, E = 1 << 24, 128
@@ -353,42 +362,51 @@ def run_count(args, peaks, peaks_kind) -> None:
                            ("zipf1.1", zipf_ids(n, E, 1.1, seed=1))):
         ref = torch.bincount(ids.long(), minlength=E)
         copies = [ids.to(dev) for _ in range(n_copies)]
-        for variant in (2, 0, 1):
+        for variant in variants:
             out = fma_b200.continuous_count(copies[0], E, _variant=variant)
             assert torch.equal(out.to(torch.int64).cpu(), ref)
             times = []
-            for i in range(args.warmup + args.steps):
+            for i in range(warmup + steps):
                 torch.cuda._sleep(400_000)  # keep the GPU busy while the timed launch is enqueued (no host gap in the interval)
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
                 fma_b200.continuous_count(copies[i % n_copies], E, _variant=variant)
                 b.record()
                 torch.cuda.synchronize()
-                if i >= args.warmup:
+                if i >= warmup:
                     times.append(a.elapsed_time(b))
             ms = float(np.median(times))
             gbs = (n * 4 + E * 4) / ms / 1e6
             results[f"{dist_name}/variant{variant}"] = {"ms": ms, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]}
         del copies
-    # streaming rate on an input 16x larger (1 GiB of ids), default variant: shows the size-independent part
-    big = torch.randint(0, E, (n * 16,), dtype=torch.int32, device=dev)
-    times = []
-    for i in range(8):
-        torch.cuda._sleep(400_000)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fma_b200.continuous_count(big, E)
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
-    big_ms = float(np.median(times[3:]))
-    results["uniform_2^28_ids/default"] = {"ms": big_ms, "gbs": n * 16 * 4 / big_ms / 1e6,
-                                           "frac": n * 16 * 4 / big_ms / 1e6 / peaks["hbm_gbs"]}
-    del big
+    if big:
+        # streaming rate on an input 16x larger (1 GiB of ids), default variant: shows the size-independent part
+        big_ids = torch.randint(0, E, (n * 16,), dtype=torch.int32, device=dev)
+        times = []
+        for i in range(8):
+            torch.cuda._sleep(400_000)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fma_b200.continuous_count(big_ids, E)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        big_ms = float(np.median(times[3:]))
+        results["uniform_2^28_ids/default"] = {"ms": big_ms, "gbs": n * 16 * 4 / big_ms / 1e6,
+                                               "frac": n * 16 * 4 / big_ms / 1e6 / peaks["hbm_gbs"]}
+        del big_ids
     t0 = time.perf_counter()
-    for _ in range(5):
+    for _ in range(3):
         torch.bincount(ids.long(), minlength=E)
-    cpu_ms = (time.perf_counter() - t0) / 5 * 1e3
+    cpu_ms = (time.perf_counter() - t0) / 3 * 1e3
+    return results, cpu_ms
+
+
+def run_count(args, peaks, peaks_kind) -> None:
+    from fma_b200 import _native
+
+    n, E = 1 << 24, 128
+    results, cpu_ms = measure_count(peaks, args.steps, args.warmup, variants=(2, 0, 1), big=True)
     best = min(results["uniform/variant0"], results["zipf1.1/variant0"], key=lambda r: r["gbs"])  # the slower distribution
     line = {
         "metric": "continuous_count_GBps", "value": best["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -397,13 +415,152 @@ def run_count(args, peaks, peaks_kind) -> None:
         "config": {"workload": "count_c2", "n": n, "bins": E, "l2": "8 rotating copies of the ids (512 MB in total, larger than L2); no launch re-reads cached data",
                    "reported": "variant 0 (the default), slower of uniform / Zipf(1.1)"},
         "roofline": {"bound": "hbm", "achieved": best["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": best["gbs"] / peaks["hbm_gbs"], "traffic": None, "peak_kind": peaks_kind},
+                     "frac": best["gbs"] / peaks["hbm_gbs"], "traffic": n * 4, "peak_kind": peaks_kind},
         "variants": results,
         "cpu_baseline": {"value": (n * 4 + E * 4) / cpu_ms / 1e6, "unit": "GB/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": "torch.bincount of the full 2^24 ids (includes the int64 cast)"},
         "gpu_launches": _native.launch_count,
     }  # fmt: skip
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# measurement pieces shared by the main workload and the extra blocks
+# ---------------------------------------------------------------------------------------------
+def measure_device_steps(layer, x, dy, steps: int, warmup: int, barrier):
+    """`warmup` untimed steps, then `steps` timed ones with inputs resident in HBM; returns (total ms by CUDA
+    events, per-entry-point event times, kernels launched inside the timed region)."""
+    from fma_b200 import _native
+
+    for _ in range(warmup):
+        layer_step(layer, x, dy)
+    barrier()
+    launches_before = _native.launch_count
+    _native.enable_timing(True)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        layer_step(layer, x, dy)
+    end.record()
+    barrier()
+    ms_total = start.elapsed_time(end)
+    kernel_times = _native.collect_timing()
+    _native.enable_timing(False)
+    return ms_total, kernel_times, _native.launch_count - launches_before
+
+
+# DRAM traffic of the six grouped-GEMM launches of one ep_c5 step on one GPU (bytes; dram__bytes_read.sum +
+# dram__bytes_write.sum per kernel, from ncu captures of single launches at T=8192 tokens with all other
+# dimensions of the workload, scaled by 8 to T=65536: traffic grows with the rows, the weights are 7 % of it).
+# None until such a capture exists for the kernels as built.
+GEMM_DRAM_TRAFFIC_EP_C5 = None
+
+
+def roofline_accounting(cfg: dict, kernel_times: dict, steps: int, ms_step: float, peaks: dict, peaks_kind: str):
+    work = algorithmic_work(cfg)
+    tensor_peak = peaks["bf16_tflops_sustained"] if cfg["dtype"] == "bf16" else None
+    kernels = {}
+    gemm_ms = 0.0
+    gemm_flops = 0
+    for name, (calls, ms) in sorted(kernel_times.items()):
+        per_step = ms / steps
+        entry = {"calls_per_step": calls / steps, "ms_per_step": per_step}
+        if name in work["gemm_flops"]:
+            # per-rank FLOPs: every rank processes T*k rows in expectation under a uniform router
+            fl = work["gemm_flops"][name]
+            entry.update(achieved=fl / per_step / 1e9, unit="TFLOP/s")
+            if tensor_peak:
+                entry["frac"] = entry["achieved"] / tensor_peak
+            gemm_ms += per_step
+            gemm_flops += fl
+        elif name in work["hbm_bytes"]:
+            by = work["hbm_bytes"][name]
+            entry.update(achieved=by / per_step / 1e6, unit="GB/s", frac=by / per_step / 1e6 / peaks["hbm_gbs"])
+        kernels[name] = entry
+    roofline = None
+    if gemm_ms > 0:
+        achieved = gemm_flops / gemm_ms / 1e9
+        traffic = GEMM_DRAM_TRAFFIC_EP_C5 if (cfg["T"], cfg["H"], cfg["E"], cfg["k"], cfg["I"]) == (65536, 4096, 128, 8, 1536) else None
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": (achieved / tensor_peak) if tensor_peak else None, "traffic": traffic,
+                    "kernel": "gemm_tc2_kernel (tcgen05 cta_group::2; 6 launches per step)" if cfg["dtype"] == "bf16"
+                    else "gemm_simt_kernel",
+                    "peak_kind": f"{peaks_kind} sustained cuBLAS bf16", "gemm_ms_per_step": gemm_ms,
+                    "gemm_share_of_step": gemm_ms / ms_step}  # fmt: skip
+    return kernels, roofline
+
+
+def extra_blocks(device: torch.device, peaks: dict, peaks_kind: str, steps: int = 5) -> dict:
+    """Short measurements of the other single-GPU configurations, outside the timed region of the main
+    workload: tokens/s and GEMM roofline fraction of the fine-grained and the Mixtral-shaped layer, GB/s of
+    continuous_count at 2^24 ids.  Device-resident inputs, `steps` timed steps after 3 warm-up steps."""
+    out = {}
+
+    def barrier():
+        torch.cuda.synchronize()
+
+    for name in ("finegrained_c4", "mixtral_c3"):
+        cfg = dict(WORKLOADS[name])
+        layer, dtype = make_layer(cfg, 0, 1, device)
+        x, dy = make_inputs(cfg, 0, device, dtype)
+        x.requires_grad_(True)
+        ms_total, kernel_times, _ = measure_device_steps(layer, x, dy, steps, 3, barrier)
+        ms_step = ms_total / steps
+        kernels, roofline = roofline_accounting(cfg, kernel_times, steps, ms_step, peaks, peaks_kind)
+        out[name] = {"value": cfg["T"] / (ms_step / 1e3), "unit": "tokens/s", "ms_per_step": ms_step, "steps": steps,
+                     "roofline_frac": roofline["frac"], "gemm_tflops": roofline["achieved"],
+                     "gemm_frac": {k[len("fma_b200_moe_gemm_"):]: round(v["frac"], 4) for k, v in kernels.items() if "gemm" in k},
+                     "hbm_frac": {k[len("fma_b200_"):]: round(v["frac"], 4) for k, v in kernels.items()
+                                  if v.get("unit") == "GB/s"}}  # fmt: skip
+        del layer, x, dy
+        torch.cuda.empty_cache()
+    results, _ = measure_count(peaks, 20, 5, variants=(0,), big=False)
+    out["count_c2"] = {"unit": "GB/s", "uniform": results["uniform/variant0"], "zipf1.1": results["zipf1.1/variant0"]}
+    return out
+
+
+def ep_parity_check(layer, cfg: dict, rank: int, world: int, device: torch.device, dtype, tokens: int = 1024) -> dict:
+    """One small untimed step through the expert-parallel layer against a single-GPU layer that holds all
+    experts (rebuilt from the same seeds) run on the tokens of all ranks: y and dx of this rank's tokens and
+    the gradients of this rank's experts.  Errors are the maximum over ranks."""
+    import torch.distributed as dist
+
+    small = dict(cfg, T=tokens)
+    x, dy = make_inputs(small, rank, device, dtype)
+    xs = [torch.empty_like(x) for _ in range(world)]
+    dys = [torch.empty_like(dy) for _ in range(world)]
+    dist.all_gather(xs, x)
+    dist.all_gather(dys, dy)
+    full, _ = make_layer(cfg, 0, 1, device)
+    x_all = torch.cat(xs).requires_grad_(True)
+    y_all, _ = full(x_all)
+    y_all.backward(torch.cat(dys))
+    lo, hi = rank * tokens, (rank + 1) * tokens
+    xr = x.clone().requires_grad_(True)
+    for p in layer.parameters():
+        p.grad = None
+    y, _ = layer(xr)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    e0, e1 = layer.local_expert_range()
+
+    def rel(a, b):
+        return float((a.double() - b.double()).norm() / b.double().norm())
+
+    errs = [rel(xr.grad, x_all.grad[lo:hi]), rel(layer.c_fc.weight.grad, full.c_fc.weight.grad[e0:e1]),
+            rel(layer.c_proj.weight.grad, full.c_proj.weight.grad[e0:e1]), rel(y, y_all.detach()[lo:hi]),
+            0.0 if torch.equal(y, y_all.detach()[lo:hi]) else 1.0]
+    t = torch.tensor(errs, device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dx, dfc, dproj, ey, y_diff = t.tolist()
+    for p in layer.parameters():
+        p.grad = None
+    del full, x_all, y_all
+    torch.cuda.empty_cache()
+    tol = 1e-2
+    return {"tokens_per_rank": tokens, "y_bit_equal": y_diff == 0.0, "y": ey, "dx": dx, "d_w_fc": dfc, "d_w_proj": dproj,
+            "tolerance": tol, "transport": layer.last_transport,
+            "ok": bool(y_diff == 0.0 and max(dx, dfc, dproj) <= tol)}  # fmt: skip
 
 
 # ---------------------------------------------------------------------------------------------
@@ -427,10 +584,15 @@ def main() -> None:
     ap.add_argument("--ep-fuse-return", action="store_true",
                     help="peer transport: the down projection and the dgrad store their tiles straight into the "
                          "senders' arenas (no return copies)")
-    ap.add_argument("--e2e-prefetch", action="store_true",
-                    help="end-to-end loop as a streaming input pipeline: the host-to-device copy of step i+1 and the "
-                         "device-to-host copy of step i's input gradient overlap the neighbouring step's kernels "
-                         "(every copy still lies inside the timed region)")
+    ap.add_argument("--e2e-serial", action="store_true",
+                    help="end-to-end loop with every step's copies issued inside that step; the default is a streaming "
+                         "input pipeline: the host-to-device copy of step i+1 and the device-to-host copy of step i's "
+                         "input gradient overlap the neighbouring step's kernels (every copy still lies inside the "
+                         "timed region)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the short extra measurements of the other single-GPU configurations (N = 1)")
+    ap.add_argument("--no-ep-parity", action="store_true",
+                    help="skip the small untimed parity step of the expert-parallel layer (N > 1)")
     ap.add_argument("--timeline", default="", metavar="FILE",
                     help="after the timed runs, record one more step with torch.profiler on rank 0 and write its "
                          "device timeline (start ms, duration ms, stream, kernel or copy) to FILE; never part of a "
@@ -489,25 +651,13 @@ def main() -> None:
     T = cfg["T"]
 
     # ---- device-resident timing -------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
     for _ in range(args.warmup):
         layer_step(layer, x, dy)
-    barrier()
-    launches_before = _native.launch_count
-    _native.enable_timing(True)
-    sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        layer_step(layer, x, dy)
-    end.record()
-    barrier()
+    ms_total, kernel_times, launches = measure_device_steps(layer, x, dy, args.steps, 0, barrier)
     clocks = sampler.stop() if rank == 0 else None
-    ms_total = start.elapsed_time(end)
-    kernel_times = _native.collect_timing()
-    _native.enable_timing(False)
-    launches = _native.launch_count - launches_before
     status = _native.device_status()
     if status != 0:
         raise SystemExit(f"a kernel reported device status {status:#x}")
@@ -593,11 +743,11 @@ def main() -> None:
             main_stream.wait_stream(out_stream)
 
         def e2e_run(n_steps: int) -> None:
-            if args.e2e_prefetch:
-                e2e_loop_prefetch(n_steps)
-            else:
+            if args.e2e_serial:
                 for _ in range(n_steps):
                     e2e_step()
+            else:
+                e2e_loop_prefetch(n_steps)
 
         e2e_run(2)
         barrier()
@@ -615,7 +765,12 @@ def main() -> None:
         nbytes = x_host.numel() * x_host.element_size()
         e2e = {"value": world * T / (e2e_ms / args.steps / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
                "d2h_bytes_per_step": 2 * nbytes, "ms_per_step": e2e_ms / args.steps,
-               "pipeline": "inputs of step i+1 prefetched during step i" if args.e2e_prefetch else "per-step copies"}  # fmt: skip
+               "pipeline": "per-step copies" if args.e2e_serial else "inputs of step i+1 prefetched during step i"}  # fmt: skip
+
+    timed_transport = layer.last_transport if world > 1 else None
+    ep_parity = None
+    if world > 1 and not args.no_ep_parity:
+        ep_parity = ep_parity_check(layer, cfg, rank, world, device, dtype)
 
     if rank != 0:
         if world > 1:
@@ -623,45 +778,18 @@ def main() -> None:
         return
 
     # ---- roofline accounting ----------------------------------------------------------------
-    work = algorithmic_work(cfg)
-    tensor_peak = peaks["bf16_tflops_sustained"] if cfg["dtype"] == "bf16" else None
-    kernels = {}
-    gemm_ms = 0.0
-    gemm_flops = 0
-    for name, (calls, ms) in sorted(kernel_times.items()):
-        per_step = ms / args.steps
-        entry = {"calls_per_step": calls / args.steps, "ms_per_step": per_step}
-        if name in work["gemm_flops"]:
-            # per-rank FLOPs: every rank processes T*k rows in expectation under a uniform router
-            fl = work["gemm_flops"][name]
-            entry.update(achieved=fl / per_step / 1e9, unit="TFLOP/s")
-            if tensor_peak:
-                entry["frac"] = entry["achieved"] / tensor_peak
-            gemm_ms += per_step
-            gemm_flops += fl
-        elif name in work["hbm_bytes"]:
-            by = work["hbm_bytes"][name]
-            entry.update(achieved=by / per_step / 1e6, unit="GB/s", frac=by / per_step / 1e6 / peaks["hbm_gbs"])
-        kernels[name] = entry
-    roofline = None
-    if gemm_ms > 0:
-        achieved = gemm_flops / gemm_ms / 1e9
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
-                    "frac": (achieved / tensor_peak) if tensor_peak else None, "traffic": None,
-                    "kernel": "gemm_tc2_kernel + gemm_tc_kernel (tcgen05; 6 launches per step)" if cfg["dtype"] == "bf16"
-                    else "gemm_simt_kernel",
-                    "peak_kind": f"{peaks_kind} sustained cuBLAS bf16", "gemm_ms_per_step": gemm_ms,
-                    "gemm_share_of_step": gemm_ms / ms_step}  # fmt: skip
+    kernels, roofline = roofline_accounting(cfg, kernel_times, args.steps, ms_step, peaks, peaks_kind)
 
     if args.timeline:
         write_timeline(args.timeline, lambda: layer_step(layer, x, dy), rank, barrier)
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
+        threads = pin_cpu_threads()
         weights = host_weights_from_layer(layer, cpu_sample(cfg)[0])
         cpu_oracle_pass(cfg, weights, seed=0, tokens=64)  # warm the BLAS threads
         secs, toks = cpu_oracle_pass(cfg, weights, seed=1)
-        cpu_baseline = {"value": toks / secs, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+        cpu_baseline = {"value": toks / secs, "unit": "tokens/s", "cores": threads, "kind": "port",
                         "sample": f"one forward+backward ({secs:.1f} s) of " + cpu_sample_text(cfg)}  # fmt: skip
 
     line = {
@@ -672,12 +800,18 @@ def main() -> None:
                    "tokens_per_gpu": T, "router": cfg["router"],
                    "parallelism": f"ep{world}" if world > 1 else "single",
                    "ep_chunks": args.ep_chunks if world > 1 else None,
-                   "ep_transport": layer.last_transport if world > 1 else None,
+                   "ep_transport": timed_transport,
                    "ep_fuse_return": bool(args.ep_fuse_return) if world > 1 else None, "sm_reserve": args.sm_reserve if world > 1 else None,
                    "l2": "inputs larger than L2 (x alone is %d MB)" % (x.numel() * x.element_size() >> 20)},
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": launches,
     }  # fmt: skip
+    if ep_parity is not None:
+        line["ep_parity"] = ep_parity
+    if world == 1 and args.workload == "ep_c5" and not args.tokens and not args.no_extra:
+        del layer, x, dy
+        torch.cuda.empty_cache()
+        line["extra"] = extra_blocks(device, peaks, peaks_kind)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -72,7 +72,7 @@ const char* fma_b200_status_string(int status) {
 
 const char* fma_b200_last_error(void) { return fmab::last_error_buffer(); }
 
-int fma_b200_abi_version(void) { return 2; }
+int fma_b200_abi_version(void) { return 3; }
 
 int fma_b200_set_sm_limit(int32_t sms) {
     fmab::set_sm_limit(sms);
@@ -87,6 +87,15 @@ int fma_b200_device_status(int32_t* status_out, void* stream) {
     FMAB_CUDA(cudaMemcpyAsync(status_out, dptr, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
     FMAB_CUDA(cudaMemsetAsync(dptr, 0, sizeof(int32_t), s));
     FMAB_CUDA(cudaStreamSynchronize(s));
+    return FMA_B200_OK;
+}
+
+int fma_b200_device_status_peek(int32_t* device_out, void* stream) {
+    FMAB_REQUIRE(device_out != nullptr, FMA_B200_ERR_BAD_ARG, "device_out is NULL");
+    int32_t* dptr = fmab::device_status_ptr();
+    FMAB_REQUIRE(dptr != nullptr, FMA_B200_ERR_LAUNCH, "no address for the device status word");
+    FMAB_CUDA(cudaMemcpyAsync(device_out, dptr, sizeof(int32_t), cudaMemcpyDeviceToDevice,
+                              static_cast<cudaStream_t>(stream)));
     return FMA_B200_OK;
 }
 

@@ -46,6 +46,14 @@ int sm_count();
 int sm_count_physical();
 void set_sm_limit(int n);
 
+// Ordinal of the current device, or -1.  Used to key per-device caches (function attributes such as the
+// dynamic shared-memory opt-in apply to the current device only).
+inline int current_device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    return dev;
+}
+
 // Device status word shared by all kernels of this library (see fma_b200_device_status).
 int32_t* device_status_ptr();
 

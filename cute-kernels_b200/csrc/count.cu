@@ -263,8 +263,10 @@ static int launch_count(const void* ids, int64_t n, int size, uint32_t* out, uin
         int warps = static_cast<int>((216 * 1024 - block_hist) / per_warp);
         warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
         const int64_t smem = block_hist + warps * per_warp;
-        static bool configured[2] = {false, false};
-        bool& conf = configured[sizeof(IdT) == 4 ? 0 : 1];
+        static bool configured[2][64] = {{false}};  // per id width and device
+        const int dev = current_device_slot();
+        FMAB_REQUIRE(dev >= 0, FMA_B200_ERR_LAUNCH, "no current CUDA device with an ordinal below 64");
+        bool& conf = configured[sizeof(IdT) == 4 ? 0 : 1][dev];
         if (!conf) {
             FMAB_CUDA(cudaFuncSetAttribute(continuous_count_private_kernel<IdT>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));

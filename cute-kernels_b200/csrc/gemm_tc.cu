@@ -21,6 +21,7 @@
 //
 // Every mbarrier wait is bounded (about one second of %globaltimer); a wait that runs out sets
 // the device status word, raises a CTA-wide abort flag that all other waits poll, and the CTA
+// leaves its role loops, frees its tensor memory and exits; the host reads the status word.
 #include <vector>
 
 #include "gemm_tc.cuh"
@@ -477,6 +478,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
     }
 }
 
+// Epilogue width: 8 warps (two per TMEM lane quadrant) by default; FMA_B200_GEMM_EPI_WARPS=4 selects
 // the narrower build (a tuning knob for measurements).
 static int epilogue_warps() {
     static int cached = 0;
@@ -492,11 +494,13 @@ static int launch_gemm_w(const GemmParams& p_in, cudaStream_t s) {
     GemmParams p = p_in;
     if (int rc = next_sched_pair(&p.sched)) return rc;
     p.dynamic_tiles = dynamic_tiles_enabled();
-    static bool configured = false;
+    static bool configured[64] = {false};  // per device: the attribute applies to the current device only
     auto kernel = gemm_tc_kernel<A_MN, B_MN, EPI, EPI_WARPS>;
-    if (!configured) {
+    const int dev = current_device_slot();
+    FMAB_REQUIRE(dev >= 0, FMA_B200_ERR_LAUNCH, "no current CUDA device with an ordinal below 64");
+    if (!configured[dev]) {
         FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
-        configured = true;
+        configured[dev] = true;
     }
     const int64_t total = static_cast<int64_t>(p.n_mtiles) * p.n_ntiles;
     if (total <= 0) return FMA_B200_OK;

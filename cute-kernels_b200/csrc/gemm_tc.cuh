@@ -78,6 +78,12 @@ struct GemmParams {
     int32_t dynamic_tiles;        // 1: tiles drawn from the global counter; 0: tile = blockIdx.x + i * gridDim.x
     int32_t pair_skew;            // CTA-pair kernel: k-blocks by which accumulator half 1 trails half 0
     const uint64_t* mtile_dst;    // EPI_PLAIN_PEER: byte address of output row 0 of every 128-row tile (pitch ldd)
+    // CTA-pair kernel, epilogues that leave through shared memory and TMA stores: 3-D maps {columns, rows,
+    // group} with 64-column x 32-row boxes of the output (map_d) and, for the SwiGLU epilogues, of the second
+    // output / the saved pre-activations (map_d2).  Rows mode uses group coordinate 0.
+    CUtensorMap map_d;
+    CUtensorMap map_d2;
+    int32_t tma_store;            // 1: the epilogue stores through map_d (and map_d2)
 };
 
 // ---------------------------------------------------------------------------
@@ -128,6 +134,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
+}
+// TMA store of a 64-column x 32-row box from shared memory (128-byte swizzle) to coordinates {c0, c1, c2}.
+// Out-of-range parts of the box are not written.  Completion is tracked by the issuing thread's bulk
+// async-group: commit, then wait (".read": the source has been read and may be overwritten).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Makes this thread's shared-memory writes visible to the async proxy (TMA) before a store is issued.
+__device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_16(uint32_t addr) {
+    uint4 w;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(addr) : "memory");
+    return w;
 }
 __device__ __forceinline__ void tensormap_acquire(const CUtensorMap* map) {
     asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -256,7 +283,27 @@ inline int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
     return FMA_B200_OK;
 }
 
-// Epilogue width: 8 warps (two per TMEM lane quadrant) by default; FMA_B200_GEMM_EPI_WARPS=4 selects
+// 3-D bf16 tensor {d0 (contiguous), d1, d2} with pitches in elements, boxes of box0 x box1 x 1, 128-byte swizzle:
+// the output maps of the epilogues that store with TMA.
+inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                     uint64_t pitch2, uint32_t box0, uint32_t box1) {
+    EncodeTiledFn fn = encode_fn();
+    FMAB_REQUIRE(fn != nullptr, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
+    FMAB_REQUIRE(aligned16(base), FMA_B200_ERR_BAD_ARG, "GEMM output is not 16-byte aligned");
+    FMAB_REQUIRE((pitch1 * 2) % 16 == 0 && (pitch2 * 2) % 16 == 0, FMA_B200_ERR_BAD_ARG,
+                 "output pitches %llu / %llu elements are not multiples of 8", (unsigned long long)pitch1,
+                 (unsigned long long)pitch2);
+    FMAB_REQUIRE(d0 >= 1 && d1 >= 1 && d2 >= 1, FMA_B200_ERR_BAD_ARG, "empty tensor for a tensor map");
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {pitch1 * 2, pitch2 * 2};
+    const cuuint32_t box[3] = {box0, box1, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FMAB_REQUIRE(r == CUDA_SUCCESS, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
+    return FMA_B200_OK;
+}
 
 // Scheduler words of the dynamic tile scheduler: 64 pairs per device, handed out round-robin so that
 // launches running concurrently on different streams do not share a pair.  Zero at load; every launch

@@ -52,8 +52,13 @@ struct PairShape {
     static constexpr int kStageBytes = A_STAGE_BYTES + HALVES * PAIR_B_BYTES;  // 16 KB + HALVES x 16 KB
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
 };
-// EPI_PLAIN_PEER stages every 32-row x 64-column piece of the output in shared memory (4 KB per epilogue
-// warp, behind the operand ring) so that it leaves the SM as whole 128-byte row segments.
+// The epilogues stage every 32-row x 64-column piece of the output in shared memory (a 4 KB patch per
+// epilogue warp, behind the operand ring) so that it leaves the SM as whole 128-byte row segments: one
+// thread per row storing straight from its registers makes every store instruction touch 32 different
+// 128-byte lines, and the load/store unit then needs about 12k cycles to drain a 256x512 tile, half as long
+// as the tile's main loop at K = 1536.  From the patch (128-byte swizzle, the layout TMA expects) the piece
+// goes out as ONE TMA store issued by one lane (EPI_PLAIN and the SwiGLU epilogues), or as eight fully
+// coalesced 512-byte store instructions where the destination is an arbitrary address (EPI_PLAIN_PEER).
 constexpr int PEER_PATCH_BYTES = 32 * 128;
 constexpr size_t PEER_PATCH_TOTAL = static_cast<size_t>(PAIR_EPI_WARPS) * PEER_PATCH_BYTES;
 
@@ -503,7 +508,42 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             const int n0h = t.n0 + h * t.n_step;                 // first D column of this half
             const int n_valid = min(t.n_step, p.n_cols - n0h);   // <= 0: the half carries no columns
 
-            if (EPI == EPI_PLAIN) {
+            if (EPI == EPI_PLAIN && p.tma_store) {
+                // registers -> swizzled patch -> one TMA store per 32 rows x 64 columns
+                const uint32_t patch = ring + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * PEER_PATCH_BYTES;
+                constexpr int kGroups = BN / 64 / 2;  // 64-column groups per warp and half
+                const int row_c = ((p.mode == MODE_ROWS) ? static_cast<int>(t.d_row) : t.a_mn) + quad * 32;
+                const int grp_c = (p.mode == MODE_ROWS) ? 0 : t.group;
+                const bool rows_here = quad * 32 < t.rows_valid;
+#pragma unroll 1
+                for (int g = half * kGroups; g < (half + 1) * kGroups; ++g) {
+                    const int cols_left = n_valid - g * 64;
+                    if (cols_left <= 0) break;
+                    if (lane == 0) bulk_wait_read_all();  // the previous store has read the patch
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        float v[32];
+                        if (any_k && cols_left > q * 32) {
+                            tc_load_32(taddr + g * 64 + q * 32, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t piece = static_cast<uint32_t>(q * 4 + k) ^ (lane & 7);
+                            st_shared_16(patch + lane * 128 + piece * 16, Elem<__nv_bfloat16>::pack(v + k * 8));
+                        }
+                    }
+                    fence_smem_to_async();
+                    __syncwarp();
+                    if (lane == 0 && rows_here) {
+                        tma_store_3d(&p.map_d, patch, n0h + g * 64, row_c, grp_c);
+                        bulk_commit();
+                    }
+                }
+            } else if (EPI == EPI_PLAIN) {
                 __nv_bfloat16* drow = p.d + grow * p.ldd + n0h;
                 constexpr int kChunks = BN / 32 / 2;
 #pragma unroll 1
@@ -641,6 +681,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             acc_phase ^= 1u;
             ++tile_count;
         }
+        if (lane == 0) bulk_wait_all();  // TMA stores of this warp (if any) are complete before the CTA retires
     }
 
     __syncwarp();
@@ -676,14 +717,34 @@ static int pair_skew() {
     return v;
 }
 
+// FMA_B200_GEMM_EPI_TMA=0 keeps the epilogues on per-row stores from registers (a measurement knob).
+static int tma_store_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* env = getenv("FMA_B200_GEMM_EPI_TMA");
+        v = (env != nullptr && atoi(env) == 0) ? 0 : 1;
+    }
+    return v;
+}
+
+// Output map of a rows-mode GEMM: [rows_cap, n_cols] with row pitch `pitch` elements.
+static int encode_rows_output(GemmParams& p, const void* D, int64_t rows_cap, int n_cols, int64_t pitch) {
+    if (!tma_store_enabled()) return FMA_B200_OK;
+    if (int rc = encode_3d(&p.map_d, D, n_cols, rows_cap, 1, pitch, pitch, 64, 32)) return rc;
+    p.tma_store = 1;
+    return FMA_B200_OK;
+}
+
 template <bool A_MN, bool B_MN, int EPI, int HALVES = 2>
 static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s) {
-    static bool configured = false;
+    static bool configured[64] = {false};  // per device: the attribute applies to the current device only
     auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI, HALVES>;
-    constexpr size_t PAIR_SMEM_BYTES = PairShape<HALVES>::kSmemBytes + (EPI == EPI_PLAIN_PEER ? PEER_PATCH_TOTAL : 0);
-    if (!configured) {
+    constexpr size_t PAIR_SMEM_BYTES = PairShape<HALVES>::kSmemBytes + PEER_PATCH_TOTAL;
+    const int dev = current_device_slot();
+    FMAB_REQUIRE(dev >= 0, FMA_B200_ERR_LAUNCH, "no current CUDA device with an ordinal below 64");
+    if (!configured[dev]) {
         FMAB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM_BYTES));
-        configured = true;
+        configured[dev] = true;
     }
     if (total_tiles <= 0) return FMA_B200_OK;
     FMAB_REQUIRE(total_tiles < (1LL << 31), FMA_B200_ERR_BAD_ARG, "too many tiles");
@@ -722,6 +783,7 @@ int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, 
     p.k_len = IN;
     p.b_group_stride = OUT;
     p.n_groups = E;
+    if (int rc = encode_rows_output(p, Y, rows_cap, OUT, OUT)) return rc;
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
     if (narrow) return launch_pair<false, false, EPI_PLAIN, 1>(p, total, s);
     return launch_pair<false, false, EPI_PLAIN>(p, total, s);
@@ -770,6 +832,9 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     p.k_len = OUT;
     p.b_group_stride = OUT;
     p.n_groups = E;
+    if (!swiglu) {
+        if (int rc = encode_rows_output(p, dX, rows_cap, IN, IN)) return rc;
+    }
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
     if (narrow) {
         if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD, 1>(p, total, s);
@@ -838,6 +903,10 @@ int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, 
     p.n_ntiles = (IN + 2 * BN - 1) / (2 * BN);
     p.n_cols = IN;
     p.n_groups = E;
+    if (tma_store_enabled()) {  // dW as {IN, OUT, E}: rows of a tile beyond OUT are clipped, not written into the next expert
+        if (int rc = encode_3d(&p.map_d, dW, IN, OUT, E, IN, static_cast<uint64_t>(OUT) * IN, 64, 32)) return rc;
+        p.tma_store = 1;
+    }
     const int64_t total = static_cast<int64_t>(E) * ((p.mtiles_per_group + 1) / 2) * p.n_ntiles;
     return launch_pair<true, true, EPI_PLAIN>(p, total, s);
 }

@@ -52,6 +52,7 @@ scatter_kernel(const T* __restrict__ x, int64_t n_tok, int H, int k, const int32
             if (c < n_vec) v[u] = ld_stream_16(src + c);
         }
         for (int j = 0; j < k; ++j) {
+            if (rows[j] < 0) continue;  // slot without a row (its expert id was out of range)
             uint4* dst = reinterpret_cast<uint4*>(grouped + static_cast<int64_t>(rows[j]) * H);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -92,6 +93,7 @@ gather_sum_kernel(const T* __restrict__ grouped, const T* __restrict__ coeff, in
         for (int j = 0; j < k; ++j) {
             const int32_t row = __shfl_sync(0xffffffffu, my_row, j);
             const float w = __shfl_sync(0xffffffffu, my_w, j);
+            if (row < 0) continue;  // slot without a row: contributes nothing
             const uint4* src = reinterpret_cast<const uint4*>(grouped + static_cast<int64_t>(row) * H);
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
@@ -132,6 +134,13 @@ combine_backward_kernel(const T* __restrict__ dy, const T* __restrict__ expert_o
     const bool want_dw = (d_weights != nullptr) && (expert_out != nullptr);
     for (int j = 0; j < k; ++j) {
         const int64_t row = row_of_slot[t * k + j];
+        if (row < 0) {  // slot without a row: no gradient row to write, zero gradient for its weight
+            if (want_dw && lane == 0) {
+                if constexpr (sizeof(T) == 2) d_weights[t * k + j] = __float2bfloat16_rn(0.f);
+                else d_weights[t * k + j] = 0.f;
+            }
+            continue;
+        }
         const T wt = weights[t * k + j];
         float w;
         if constexpr (sizeof(T) == 2) w = __bfloat162float(wt); else w = wt;

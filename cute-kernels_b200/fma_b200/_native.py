@@ -28,15 +28,22 @@ SIGNATURES: dict[str, tuple] = {
     "fma_b200_abi_version": (ctypes.c_int, []),
     "fma_b200_set_sm_limit": (ctypes.c_int, [_I32]),
     "fma_b200_device_status": (ctypes.c_int, [_P, _P]),
+    "fma_b200_device_status_peek": (ctypes.c_int, [_P, _P]),
     "fma_b200_continuous_count_workspace_bytes": (_I64, [_I32]),
     "fma_b200_continuous_count": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P, _I64, _P]),
     "fma_b200_continuous_count_variant": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P, _I64, _I32, _P]),
     "fma_b200_continuous_count_static": (ctypes.c_int, [_P, _I32, _I64, _I32, _P, _P]),
     "fma_b200_router_topk_softmax": (ctypes.c_int, [_P, _I32, _I64, _I32, _I32, _P, _P, _P]),
+    "fma_b200_router_topk_softmax_routed": (ctypes.c_int, [_P, _I32, _I64, _I32, _I32, _P, _P, _I32, _P, _I64, _P]),
     "fma_b200_router_topk_softmax_backward": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _P, _P]),
+    "fma_b200_router_mean_prob_backward": (ctypes.c_int, [_P, _P, _I32, _I64, _I32, _P, _P]),
     "fma_b200_moe_rows_cap": (_I64, [_I64, _I32, _I32]),
     "fma_b200_moe_sort_workspace_bytes": (_I64, [_I64, _I32]),
     "fma_b200_moe_sort": (ctypes.c_int, [_P, _I64, _I32, _I32, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _P]),
+    "fma_b200_moe_sort_routed": (
+        ctypes.c_int,
+        [_P, _I64, _I32, _I32, _I32, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _P],
+    ),
     "fma_b200_moe_ep_recv_maps": (ctypes.c_int, [_P, _I32, _I32, _I32, _I64, _P, _P, _P]),
     "fma_b200_moe_scatter": (ctypes.c_int, [_P, _I32, _I64, _I32, _I32, _P, _P, _P, _I32, _I64, _P, _P]),
     "fma_b200_moe_scatter_backward": (ctypes.c_int, [_P, _I32, _I64, _I32, _I32, _P, _P, _P]),
@@ -97,7 +104,7 @@ def lib() -> ctypes.CDLL:
 
 # Kernels launched per entry-point call (the sort is three kernels; status queries launch none).
 KERNELS_PER_CALL = {
-    "fma_b200_moe_sort": 3, "fma_b200_device_status": 0, "fma_b200_set_sm_limit": 0, "fma_b200_peer_buffer_create": 0,
+    "fma_b200_moe_sort": 3, "fma_b200_moe_sort_routed": 2, "fma_b200_device_status": 0, "fma_b200_device_status_peek": 0, "fma_b200_set_sm_limit": 0, "fma_b200_peer_buffer_create": 0,
     "fma_b200_peer_buffer_open": 0, "fma_b200_peer_buffer_close": 0, "fma_b200_peer_buffer_destroy": 0,
     "fma_b200_peer_copy": 0,
 }  # fmt: skip

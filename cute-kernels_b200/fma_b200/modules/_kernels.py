@@ -28,6 +28,32 @@ class RowMaps:
     row_align: int = ROW_ALIGN
     sorted_expert_idxs: torch.Tensor | None = None  # int64 [R]
     sorted_scattered_idxs: torch.Tensor | None = None  # int64 [R]
+    router_mean_prob: torch.Tensor | None = None  # float32 [E], when the router pass collected it
+
+
+def device_status_peek(device: torch.device) -> torch.Tensor:
+    """int32[1] device tensor holding a copy of the library's device status word (0 = no kernel reported an
+    error), taken on the current stream without a host synchronisation and without clearing the word."""
+    out = torch.empty(1, dtype=torch.int32, device=device)
+    call("fma_b200_device_status_peek", ptr(out), stream_ptr(device))
+    return out
+
+
+STATUS_TEXT = {0x7001: "a grouped-GEMM barrier wait ran out", 0x7002: "a wait for a peer's rows ran out",
+               0x7003: "the expert sort met an expert id outside [0, E)"}
+
+
+def raise_for_device_status(codes, where: str) -> None:
+    """`codes`: status words (one per rank, or one).  Clears the local word and raises if any is non-zero."""
+    bad = {r: c for r, c in enumerate(codes) if c != 0}
+    if not bad:
+        return
+    try:
+        _native.device_status()  # clears the word so that the next step starts clean
+    except RuntimeError:
+        pass  # the error below is the one to report
+    detail = ", ".join(f"rank {r}: {c:#x} ({STATUS_TEXT.get(c, 'unknown code')})" for r, c in bad.items())
+    raise RuntimeError(f"{where}: a kernel recorded a device-side error in the previous step - {detail}")
 
 
 def rows_cap(R: int, E: int, row_align: int = ROW_ALIGN) -> int:
@@ -44,6 +70,36 @@ def router_topk_softmax(logits: torch.Tensor, k: int) -> tuple[torch.Tensor, tor
     return weights, selected
 
 
+def sort_workspace_bytes(R: int, E: int) -> int:
+    return int(_native.lib().fma_b200_moe_sort_workspace_bytes(R, E))
+
+
+def router_topk_softmax_routed(logits: torch.Tensor, k: int, want_probs: bool = False):
+    """Top-k + softmax that also leaves the expert sort's first pass (and, with want_probs, the per-expert
+    sums of the full softmax) in a workspace.  Returns (weights, selected, workspace): hand the workspace to
+    moe_sort(..., routed_workspace=workspace) for the same `selected`."""
+    T, E = logits.shape
+    logits = logits.contiguous()
+    weights = torch.empty(T, k, dtype=logits.dtype, device=logits.device)
+    selected = torch.empty(T, k, dtype=torch.int64, device=logits.device)
+    ws_bytes = sort_workspace_bytes(T * k, E)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=logits.device)
+    call("fma_b200_router_topk_softmax_routed", ptr(logits), dtype_code(logits.dtype), T, E, k, ptr(weights),
+         ptr(selected), int(want_probs), ptr(ws), ws_bytes, stream_ptr(logits.device))  # fmt: skip
+    return weights, selected, ws
+
+
+def router_mean_prob_backward(logits: torch.Tensor, d_mean_prob: torch.Tensor) -> torch.Tensor:
+    """d_logits of mean_prob[e] = mean_t softmax(logits[t,:])[e] for an upstream gradient d_mean_prob [E]."""
+    T, E = logits.shape
+    logits = logits.contiguous()
+    d_mean_prob = d_mean_prob.to(torch.float32).contiguous()
+    d_logits = torch.empty_like(logits)
+    call("fma_b200_router_mean_prob_backward", ptr(logits), ptr(d_mean_prob), dtype_code(logits.dtype), T, E,
+         ptr(d_logits), stream_ptr(logits.device))  # fmt: skip
+    return d_logits
+
+
 def router_topk_softmax_backward(weights, d_weights, selected, E: int) -> torch.Tensor:
     T, k = weights.shape
     d_logits = torch.empty(T, E, dtype=weights.dtype, device=weights.device)
@@ -52,8 +108,11 @@ def router_topk_softmax_backward(weights, d_weights, selected, E: int) -> torch.
     return d_logits
 
 
-def moe_sort(selected: torch.Tensor, E: int, *, want_sorted: bool = False, row_align: int = ROW_ALIGN) -> RowMaps:
-    """Stable counting sort of the selected expert ids [T,k] and the row maps of the grouped layout."""
+def moe_sort(selected: torch.Tensor, E: int, *, want_sorted: bool = False, row_align: int = ROW_ALIGN,
+             routed_workspace: torch.Tensor | None = None, want_mean_prob: bool = False) -> RowMaps:
+    """Stable counting sort of the selected expert ids [T,k] and the row maps of the grouped layout.
+    `routed_workspace` is the workspace that router_topk_softmax_routed filled for these very ids (the
+    histogram pass is then skipped); with want_mean_prob the router's mean probabilities are reduced too."""
     assert selected.dtype == torch.int64
     selected = selected.contiguous()
     dev = selected.device
@@ -67,13 +126,22 @@ def moe_sort(selected: torch.Tensor, E: int, *, want_sorted: bool = False, row_a
     mtile_expert = torch.empty(cap // 128, dtype=torch.int32, device=dev) if row_align % 128 == 0 else None
     sorted_e = torch.empty(R, dtype=torch.int64, device=dev) if want_sorted else None
     sorted_s = torch.empty(R, dtype=torch.int64, device=dev) if want_sorted else None
-    ws_bytes = int(_native.lib().fma_b200_moe_sort_workspace_bytes(R, E))
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    call("fma_b200_moe_sort", ptr(selected), R, E, row_align, cap, ptr(sorted_e), ptr(sorted_s), ptr(expert_count),
-         ptr(pad_offsets), ptr(row_of_slot), ptr(slot_of_row), ptr(mtile_expert), ptr(ws), ws_bytes,
-         stream_ptr(dev))  # fmt: skip
+    ws_bytes = sort_workspace_bytes(R, E)
+    mean_prob = None
+    if routed_workspace is not None:
+        assert selected.dim() == 2 and routed_workspace.numel() >= ws_bytes
+        if want_mean_prob:
+            mean_prob = torch.empty(E, dtype=torch.float32, device=dev)
+        call("fma_b200_moe_sort_routed", ptr(selected), selected.size(0), top_k, E, row_align, cap, ptr(sorted_e),
+             ptr(sorted_s), ptr(expert_count), ptr(pad_offsets), ptr(row_of_slot), ptr(slot_of_row), ptr(mtile_expert),
+             ptr(mean_prob), ptr(routed_workspace), routed_workspace.numel(), stream_ptr(dev))  # fmt: skip
+    else:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        call("fma_b200_moe_sort", ptr(selected), R, E, row_align, cap, ptr(sorted_e), ptr(sorted_s), ptr(expert_count),
+             ptr(pad_offsets), ptr(row_of_slot), ptr(slot_of_row), ptr(mtile_expert), ptr(ws), ws_bytes,
+             stream_ptr(dev))  # fmt: skip
     return RowMaps(expert_count, pad_offsets, row_of_slot, slot_of_row, mtile_expert, cap, E, top_k, row_align, sorted_e,
-                   sorted_s)
+                   sorted_s, mean_prob)
 
 
 def scatter(x: torch.Tensor, maps: RowMaps) -> torch.Tensor:

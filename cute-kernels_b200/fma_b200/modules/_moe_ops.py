@@ -21,15 +21,18 @@ def _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k: int, row_a
 
 # ---- router: top-k + softmax ---------------------------------------------------------------------
 @torch.library.custom_op(f"{LIBRARY_NAME}::moe_route", mutates_args=())
-def moe_route(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor]:
+def moe_route(logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (weights, selected, workspace); the workspace carries the expert sort's first pass to
+    moe_swiglu_experts."""
     with torch.cuda.device(logits.device):
-        return K.router_topk_softmax(logits, top_k)
+        return K.router_topk_softmax_routed(logits, top_k)
 
 
 @moe_route.register_fake
 def _(logits, top_k):
-    T = logits.size(0)
-    return logits.new_empty(T, top_k), logits.new_empty((T, top_k), dtype=torch.int64)
+    T, E = logits.shape
+    return (logits.new_empty(T, top_k), logits.new_empty((T, top_k), dtype=torch.int64),
+            logits.new_empty(K.sort_workspace_bytes(T * top_k, E), dtype=torch.uint8))  # fmt: skip
 
 
 @torch.library.custom_op(f"{LIBRARY_NAME}::moe_route_backward", mutates_args=())
@@ -46,12 +49,12 @@ def _(weights, d_weights, selected, num_experts):
 
 def _route_setup(ctx, inputs, output):
     logits, _ = inputs
-    weights, selected = output
+    weights, selected, _workspace = output
     ctx.save_for_backward(weights, selected)
     ctx.num_experts = logits.size(1)
 
 
-def _route_backward(ctx, d_weights, _d_selected):
+def _route_backward(ctx, d_weights, _d_selected, _d_workspace):
     weights, selected = ctx.saved_tensors
     return moe_route_backward(weights, d_weights.contiguous(), selected, ctx.num_experts), None
 
@@ -62,14 +65,14 @@ torch.library.register_autograd(f"{LIBRARY_NAME}::moe_route", _route_backward, s
 # ---- experts: scatter -> up projection + SwiGLU -> down projection -> weighted combine ------------
 @torch.library.custom_op(f"{LIBRARY_NAME}::moe_swiglu_experts", mutates_args=())
 def moe_swiglu_experts(
-    x: torch.Tensor, weights: torch.Tensor, selected: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
-    row_align: int,
+    x: torch.Tensor, weights: torch.Tensor, selected: torch.Tensor, route_workspace: torch.Tensor, w_fc: torch.Tensor,
+    w_proj: torch.Tensor, row_align: int,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor]:  # fmt: skip
     """Returns (y, xg, pre, act, out, expert_count, pad_offsets, row_of_slot, slot_of_row, mtile_expert)."""
     with torch.cuda.device(x.device):
         x, weights, w_fc, w_proj = x.contiguous(), weights.contiguous(), w_fc.contiguous(), w_proj.contiguous()
-        maps = K.moe_sort(selected, w_fc.size(0), row_align=row_align)
+        maps = K.moe_sort(selected, w_fc.size(0), row_align=row_align, routed_workspace=route_workspace)
         xg = K.scatter(x, maps)
         pre, act = K.gemm_forward_swiglu(xg, w_fc, maps.mtile_expert, keep_pre=True, row_align=row_align)
         out = K.gemm_forward(act, w_proj, maps.mtile_expert, row_align)
@@ -79,7 +82,7 @@ def moe_swiglu_experts(
 
 
 @moe_swiglu_experts.register_fake
-def _(x, weights, selected, w_fc, w_proj, row_align):
+def _(x, weights, selected, route_workspace, w_fc, w_proj, row_align):
     T, H = x.shape
     E, two_i, _ = w_fc.shape
     R = selected.numel()
@@ -124,17 +127,17 @@ def _(dy, xg, pre, act, out, weights, w_fc, w_proj, pad_offsets, row_of_slot, sl
 
 
 def _experts_setup(ctx, inputs, output):
-    _x, weights, _selected, w_fc, w_proj, row_align = inputs
+    _x, weights, _selected, _route_workspace, w_fc, w_proj, row_align = inputs
     _y, xg, pre, act, out, _count, pad_offsets, row_of_slot, slot_of_row, mtile_expert = output
     ctx.save_for_backward(xg, pre, act, out, weights, w_fc, w_proj, pad_offsets, row_of_slot, slot_of_row, mtile_expert)
     ctx.row_align = row_align
 
 
 def _experts_backward(ctx, dy, *_unused):
-    need_x, need_weights, _, need_fc, need_proj, _ = ctx.needs_input_grad
+    need_x, need_weights, _, _, need_fc, need_proj, _ = ctx.needs_input_grad
     d_x, d_w, d_w_fc, d_w_proj = moe_swiglu_experts_backward(
         dy, *ctx.saved_tensors, ctx.row_align, need_x, need_weights, need_fc, need_proj)  # fmt: skip
-    return (d_x if need_x else None, d_w if need_weights else None, None, d_w_fc if need_fc else None,
+    return (d_x if need_x else None, d_w if need_weights else None, None, None, d_w_fc if need_fc else None,
             d_w_proj if need_proj else None, None)  # fmt: skip
 
 

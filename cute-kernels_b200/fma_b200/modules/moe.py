@@ -29,20 +29,37 @@ from . import _kernels as K
 
 
 class _RouterTopK(torch.autograd.Function):
-    """(weights, selected) = softmax(topk(logits)); backward scatters into d_logits."""
+    """(weights, selected, sort workspace) = softmax(topk(logits)); backward scatters into d_logits.
+    The workspace holds the first pass of the expert sort (and the router's probability sums when asked
+    for), produced by the same kernel."""
 
     @staticmethod
-    def forward(ctx, logits: torch.Tensor, k: int):
-        weights, selected = K.router_topk_softmax(logits, k)
+    def forward(ctx, logits: torch.Tensor, k: int, want_probs: bool):
+        weights, selected, workspace = K.router_topk_softmax_routed(logits, k, want_probs)
         ctx.save_for_backward(weights, selected)
         ctx.num_experts = logits.size(1)
-        ctx.mark_non_differentiable(selected)
-        return weights, selected
+        ctx.mark_non_differentiable(selected, workspace)
+        return weights, selected, workspace
 
     @staticmethod
-    def backward(ctx, d_weights, _d_selected):
+    def backward(ctx, d_weights, _d_selected, _d_workspace):
         weights, selected = ctx.saved_tensors
-        return K.router_topk_softmax_backward(weights, d_weights, selected, ctx.num_experts), None
+        return K.router_topk_softmax_backward(weights, d_weights, selected, ctx.num_experts), None, None
+
+
+class _RouterMeanProb(torch.autograd.Function):
+    """mean_prob[e] = mean over tokens of softmax(router_logits)[t, e].  The value comes from the router
+    kernel (passed in); this node only supplies its gradient with respect to the logits."""
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, mean_prob: torch.Tensor):
+        ctx.save_for_backward(logits)
+        return mean_prob.clone()
+
+    @staticmethod
+    def backward(ctx, d_mean_prob):
+        (logits,) = ctx.saved_tensors
+        return K.router_mean_prob_backward(logits, d_mean_prob), None
 
 
 class _Scatter(torch.autograd.Function):
@@ -263,6 +280,10 @@ class MoE(nn.Module):
             std=std,
         )
 
+        # Set to True to make every forward also produce the router statistics of a load-balancing loss
+        # (see load_balancing_loss); they come out of the routing kernels at no extra pass over the logits.
+        self.collect_router_stats = False
+
         self.act = activation_function
         # decided once, outside any compiled region: can the activation run inside the GEMM epilogue?
         self._act_is_swiglu_packed = _is_swiglu_packed(activation_function)
@@ -302,22 +323,56 @@ class MoE(nn.Module):
         if not (self.is_glu and self._act_is_swiglu_packed and self.c_fc.bias is None and self.c_proj.bias is None):
             raise NotImplementedError("torch.compile covers MoE with swiglu_packed experts and no bias")
         router_logits = self.gate(hidden_states)
-        router_weights, selected_experts = _moe_ops.moe_route(router_logits, self.top_k)
-        outputs = _moe_ops.moe_swiglu_experts(hidden_states, router_weights, selected_experts, self.c_fc.weight,
-                                              self.c_proj.weight, K.ROW_ALIGN)  # fmt: skip
+        router_weights, selected_experts, route_workspace = _moe_ops.moe_route(router_logits, self.top_k)
+        outputs = _moe_ops.moe_swiglu_experts(hidden_states, router_weights, selected_experts, route_workspace,
+                                              self.c_fc.weight, self.c_proj.weight, K.ROW_ALIGN)  # fmt: skip
         return outputs[0].view(original_shape), router_logits
 
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
         router_logits = self.gate(hidden_states)
-        router_weights, selected_experts = _RouterTopK.apply(router_logits, self.top_k)
+        router_weights, selected_experts, workspace = _RouterTopK.apply(
+            router_logits, self.top_k, bool(getattr(self, "collect_router_stats", False)))  # fmt: skip
+        # by-products of the routing kernel for the sort of exactly these ids (see _sort_selected)
+        self._routed = (selected_experts, workspace, router_logits)
         return router_logits, router_weights, selected_experts
+
+    def _sort_selected(self, selected_experts: torch.Tensor) -> K.RowMaps:
+        """Row maps for `selected_experts`; reuses what the routing kernel prepared when these are the ids
+        it produced in this forward."""
+        routed = getattr(self, "_routed", None)
+        self._routed = None
+        self.last_router_stats = None
+        with torch.no_grad():
+            if routed is None or routed[0] is not selected_experts:
+                return K.moe_sort(selected_experts, self.num_experts)
+            want = bool(getattr(self, "collect_router_stats", False))
+            maps = K.moe_sort(selected_experts, self.num_experts, routed_workspace=routed[1], want_mean_prob=want)
+        if maps.router_mean_prob is not None:
+            logits = routed[2]
+            mean_prob = maps.router_mean_prob
+            if logits.requires_grad and torch.is_grad_enabled():
+                mean_prob = _RouterMeanProb.apply(logits, mean_prob)
+            self.last_router_stats = {"tokens_per_expert": maps.expert_count, "mean_router_prob": mean_prob,
+                                      "num_tokens": selected_experts.size(0)}  # fmt: skip
+        return maps
+
+    def load_balancing_loss(self) -> torch.Tensor:
+        """num_experts * sum_e f_e * P_e for the most recent forward (needs collect_router_stats = True):
+        f_e = tokens routed to expert e / tokens, P_e = mean over tokens of softmax(router_logits)[t, e].
+        This is the auxiliary loss a caller of the reference builds from the returned router_logits
+        (fma/modules/moe/__init__.py:189); here both factors come from the routing kernels.  Differentiable
+        with respect to the router logits through P_e (f_e is a count)."""
+        stats = getattr(self, "last_router_stats", None)
+        if stats is None:
+            raise RuntimeError("set collect_router_stats = True before the forward pass")
+        f = stats["tokens_per_expert"].to(torch.float32) / float(max(stats["num_tokens"], 1))
+        return self.num_experts * torch.sum(f * stats["mean_router_prob"])
 
     def _compute_experts(
         self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor
     ) -> torch.Tensor:
         T = hidden_states.size(0)
-        with torch.no_grad():
-            maps = K.moe_sort(selected_experts, self.num_experts)
+        maps = self._sort_selected(selected_experts)
         self.last_row_maps = maps  # expert_count etc. for callers that log load balance
 
         fused = (

@@ -159,7 +159,9 @@ class _EPFusedSwigluExperts(torch.autograd.Function):
         comm = _comm_stream(dev)
 
         recv_counts = exchange_counts(maps.expert_count, world_size, group)
-        both = torch.cat([maps.expert_count.to(torch.int32), recv_counts.reshape(-1)]).tolist()  # the one host sync
+        both = torch.cat([maps.expert_count.to(torch.int32), recv_counts.reshape(-1),
+                          K.device_status_peek(dev)]).tolist()  # the one host sync; the status word rides along
+        K.raise_for_device_status(both[-1:], "expert-parallel MoE")
         E = maps.num_experts
         plan = _ChunkPlan(both[:E], [both[E + s * E_local : E + (s + 1) * E_local] for s in range(world_size)],
                           world_size, n_chunks)
@@ -294,6 +296,18 @@ class _EPFusedSwigluExperts(torch.autograd.Function):
         return d_x, d_w, d_w_fc, d_w_proj, None, None, None, None
 
 
+def peer_decision(table: list[list[int]], E: int) -> str:
+    """What every rank does with the gathered rows [counts (E), rows_cap, arena in use, transport given up,
+    status]: "unavailable" if any rank has given the peer transport up, "busy" if any rank's arena is still
+    held by a pending backward (all ranks then take NCCL for this call), else "peer".  A pure function of
+    the gathered table, so all ranks agree."""
+    if any(row[E + 2] for row in table):
+        return "unavailable"
+    if any(row[E + 1] for row in table):
+        return "busy"
+    return "peer"
+
+
 class ExpertParallelMoE(MoE):
     """`MoE` whose experts are sharded over `process_group`.  `num_experts` is the GLOBAL expert count;
     this rank allocates num_experts / world_size of them.  With a group of size 1 it is `MoE`."""
@@ -345,12 +359,11 @@ class ExpertParallelMoE(MoE):
             return super()._compute_experts(hidden_states, router_weights, selected_experts)
         if not (self.is_glu and _is_swiglu_packed(self.act) and self.c_fc.bias is None):
             raise NotImplementedError("expert parallelism is implemented for SwiGLU experts without bias")
-        with torch.no_grad():
-            maps = K.moe_sort(selected_experts, self.num_experts)
+        maps = self._sort_selected(selected_experts)
         self.last_row_maps = maps
         # "auto" takes the peer-memory transport only for the group size it has been validated on
         use_peer = self.transport == "peer" or (self.transport == "auto" and self.ep_size <= PEER_AUTO_MAX_RANKS)
-        if use_peer and self._peer_unavailable is None:
+        if use_peer:  # decided from the configuration alone: every rank enters the gather below or none does
             y = self._compute_experts_peer(hidden_states, router_weights, maps)
             if y is not None:
                 self.last_transport = "peer"
@@ -362,25 +375,34 @@ class ExpertParallelMoE(MoE):
 
     def _compute_experts_peer(self, hidden_states, router_weights, maps):
         """The layer over the peer-memory transport, or None when this call has to use NCCL: the arenas
-        cannot be set up (transport="auto"), the previous forward's arena contents are still needed by a
-        backward that has not run, or a rank would receive more rows than its arena holds.  Every rank
-        takes the same decision, from the same gathered numbers."""
+        cannot be set up (transport="auto"), some rank's arena contents are still needed by a backward that
+        has not run, or a rank would receive more rows than its arena holds.  Every rank takes the same
+        decision: everything it depends on - the counts, the row capacity, and each rank's local state
+        (arena in use, transport given up) - is in the row that the ranks gather.  The library's device
+        status word rides along: if a kernel of the previous step recorded an error (a wait for a peer's
+        rows that ran out, say), every rank raises instead of computing on rows that never arrived."""
         from . import moe_ep_peer as P
 
         dev = hidden_states.device
         E, ws = self.num_experts, self.ep_size
-        info = torch.cat([maps.expert_count.to(torch.int32),
-                          torch.full((1,), maps.rows_cap, dtype=torch.int32, device=dev)])  # fmt: skip
-        gathered = torch.empty(ws, E + 1, dtype=torch.int32, device=dev)
+        arena = self._arena
+        local_state = [maps.rows_cap, int(arena is not None and arena.busy), int(self._peer_unavailable is not None)]
+        info = torch.cat([maps.expert_count.to(torch.int32), torch.tensor(local_state, dtype=torch.int32).to(dev, non_blocking=True),
+                          K.device_status_peek(dev)])  # fmt: skip
+        gathered = torch.empty(ws, E + 4, dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(gathered, info, group=self.process_group)
         table = gathered.tolist()  # the one host synchronisation of the layer
+        K.raise_for_device_status([row[E + 3] for row in table], "expert-parallel MoE (peer transport)")
+        decision = peer_decision(table, E)
+        if decision == "unavailable":
+            self._peer_unavailable = self._peer_unavailable or "another rank has given up the peer transport"
+            return None
+        if decision == "busy":
+            return None
         counts = [row[:E] for row in table]
         need = max(row[E] for row in table)
-        arena = self._arena
         H, dtype = hidden_states.size(1), hidden_states.dtype
         if arena is None or arena.send_cap < need or arena.hidden != H or arena.dtype != dtype:
-            if arena is not None and arena.busy:
-                return None
             if arena is not None:
                 arena.close()
                 self._arena = None
@@ -393,7 +415,7 @@ class ExpertParallelMoE(MoE):
                 self._peer_unavailable = str(e)
                 return None
         plan = P.PeerPlan(counts, self.ep_rank, self.overlap_chunks)
-        if arena.busy or max(plan.total_recv_rows) > arena.recv_cap:
+        if max(plan.total_recv_rows) > arena.recv_cap:  # the same plan on every rank
             return None
         return P._EPPeerSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
                                             arena, plan, gathered[:, :E].contiguous(), self.fuse_return)  # fmt: skip

@@ -57,6 +57,13 @@ int fma_b200_set_sm_limit(int32_t sms);
  * fma/ops/grouped_gemm/cuda_implementation/kernel.cu:327-333).
  */
 int fma_b200_device_status(int32_t* status_out, void* stream);
+/*
+ * The same word without a host synchronisation: copies it (asynchronously, on `stream`) into the int32 at
+ * device_out, a DEVICE address, and leaves it as it is.  For callers that already read some device data
+ * back once per step and want the status to ride along.  Codes: 0x7001 a grouped-GEMM wait ran out,
+ * 0x7002 a peer_wait ran out, 0x7003 the expert sort met an id outside [0,E).  No reference counterpart.
+ */
+int fma_b200_device_status_peek(int32_t* device_out, void* stream);
 
 /* ======================================================================= */
 /* continuous_count                                                         */
@@ -122,6 +129,22 @@ int fma_b200_continuous_count_static(const void* ids, int32_t id_bytes, int64_t 
 int fma_b200_router_topk_softmax(const void* logits, int32_t dtype, int64_t T, int32_t E, int32_t k,
                                  void* weights, int64_t* selected, void* stream);
 /*
+ * NaN logits order as the largest value (what torch.topk does), lowest expert id first among them, so
+ * `selected` always holds k distinct ids in [0,E); the weights of such a row are NaN, as the reference's
+ * softmax makes them.
+ *
+ * The same pass with the by-products the next steps of the layer need, so that the logits and the selected
+ * ids are not read again (same reference lines, plus continuous_count / sort in MoE._compute_experts,
+ * fma/modules/moe/__init__.py:213-217, and the router_logits the caller turns into a load-balancing loss,
+ * :189): the per-warp histograms of the selected ids, which are the first pass of the expert sort, and -
+ * with want_probs != 0 - per-expert partial sums of softmax(logits[t,:]) over all E experts.  Both land in
+ * `sort_workspace` (fma_b200_moe_sort_workspace_bytes(T*k, E) bytes); pass that workspace unchanged to
+ * fma_b200_moe_sort_routed with the same T, k and E.
+ */
+int fma_b200_router_topk_softmax_routed(const void* logits, int32_t dtype, int64_t T, int32_t E, int32_t k,
+                                        void* weights, int64_t* selected, int32_t want_probs, void* sort_workspace,
+                                        int64_t workspace_bytes, void* stream);
+/*
  * Backward of the above: d_logits[T,E] (fully written; zero outside the selected
  * columns) from d_weights[T,k]:  d_tv = w * (d_w - sum_j d_w*w) in fp32, scattered
  * to the selected columns.  Stands in for autograd through F.softmax/topk
@@ -130,6 +153,15 @@ int fma_b200_router_topk_softmax(const void* logits, int32_t dtype, int64_t T, i
 int fma_b200_router_topk_softmax_backward(const void* weights, const void* d_weights, const int64_t* selected,
                                           int32_t dtype, int64_t T, int32_t E, int32_t k, void* d_logits,
                                           void* stream);
+/*
+ * Backward of mean_prob[e] = (1/T) sum_t softmax(logits[t,:])[e] (the router statistic that
+ * fma_b200_moe_sort_routed returns): d_logits[t,c] = p[t,c] * (g[c] - sum_e g[e]*p[t,e]) / T with
+ * g = d_mean_prob (fp32 [E]); the softmax is recomputed from the logits.  Stands in for autograd through
+ * the softmax a caller applies to the router_logits that MoE.forward returns
+ * (fma/modules/moe/__init__.py:189) when it forms a load-balancing loss.  d_logits [T,E] dtype, fully written.
+ */
+int fma_b200_router_mean_prob_backward(const void* logits, const float* d_mean_prob, int32_t dtype, int64_t T,
+                                       int32_t E, void* d_logits, void* stream);
 
 /* ======================================================================= */
 /* expert sort + row maps                                                   */
@@ -157,8 +189,16 @@ int fma_b200_router_topk_softmax_backward(const void* weights, const void* d_wei
  *   mtile_expert           int32[rows_cap/128]  expert that owns each 128-row tile, -1 beyond
  *                                     the last used tile (only when row_align % 128 == 0)
  * rows_cap must be >= fma_b200_moe_rows_cap(R, E, row_align).
- * workspace: fma_b200_moe_sort_workspace_bytes(R, E) bytes.
- * `selected` values must lie in [0,E); E <= 1024.
+ * workspace: fma_b200_moe_sort_workspace_bytes(R, E) bytes, 4-byte aligned, contents irrelevant.
+ * `selected` values should lie in [0,E); E <= 1024.  An id outside the range is never used as an index:
+ * it is left out of the counts and of the sorted outputs, its row_of_slot entry is -1 (the scatter /
+ * combine kernels skip such slots) and code 0x7003 is recorded in the device status word.
+ *
+ * fma_b200_moe_sort_routed is the same sort for ids that fma_b200_router_topk_softmax_routed selected
+ * (R = T*k): the histogram pass is skipped because that call left it in `workspace`.  If
+ * router_mean_prob is not NULL (and the router call had want_probs != 0) it also receives
+ * float32[E]: the mean over the T tokens of softmax(logits[t,:])[e], summed in a fixed order
+ * (deterministic); together with expert_count these are the two factors of the usual load-balancing loss.
  */
 int64_t fma_b200_moe_rows_cap(int64_t R, int32_t E, int32_t row_align);
 int64_t fma_b200_moe_sort_workspace_bytes(int64_t R, int32_t E);
@@ -166,6 +206,11 @@ int fma_b200_moe_sort(const int64_t* selected, int64_t R, int32_t E, int32_t row
                       int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, uint32_t* expert_count,
                       int32_t* pad_offsets, int32_t* row_of_slot, int32_t* slot_of_row, int32_t* mtile_expert,
                       void* workspace, int64_t workspace_bytes, void* stream);
+int fma_b200_moe_sort_routed(const int64_t* selected, int64_t T, int32_t k, int32_t E, int32_t row_align,
+                             int64_t rows_cap, int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs,
+                             uint32_t* expert_count, int32_t* pad_offsets, int32_t* row_of_slot, int32_t* slot_of_row,
+                             int32_t* mtile_expert, float* router_mean_prob, void* workspace, int64_t workspace_bytes,
+                             void* stream);
 
 /*
  * Row maps for rows received from other ranks under expert parallelism: `counts` is
@@ -275,7 +320,7 @@ int fma_b200_swiglu_backward(const void* gate, int64_t gate_pitch, const void* u
  * IN and OUT must be multiples of 8; all pointers 16-byte aligned.
  * row_align is the alignment the grouped rows were sorted with (fma_b200_moe_sort's row_align, or the
  * one given to fma_b200_moe_ep_recv_maps): with a multiple of 256 the bf16 kernels run on CTA pairs
- * (tcgen05 cta_group::2, one 256x256 tile per two SMs); with 128 on single CTAs (128x256 tiles).
+ * (tcgen05 cta_group::2, one 256x512 tile per two SMs); with 128 on single CTAs (128x256 tiles).
  */
 int fma_b200_moe_gemm_forward(const void* X, const void* W, void* Y, int32_t dtype, int64_t rows_cap, int32_t E,
                               int32_t OUT, int32_t IN, const int32_t* mtile_expert, int32_t row_align, void* stream);

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
         assert name in _native.SIGNATURES, f"{name} has no ctypes signature"
     assert sorted(_native.SIGNATURES) == names
-    assert lib.fma_b200_abi_version() == 2
+    assert lib.fma_b200_abi_version() == 3
 
 
 def test_status_strings_and_bad_arguments_without_gpu():

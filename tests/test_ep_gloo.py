@@ -175,3 +175,23 @@ def test_chunk_bounds_cover_all_experts():
                 sizes = [y - x for x, y in zip(b, b[1:])]
                 assert sizes[0] == sizes[-1] == max(1, experts // 16)
                 assert max(sizes[1:-1]) - min(sizes[1:-1]) <= 1
+
+
+def test_transport_decision_is_a_function_of_the_gathered_table_only():
+    """Ranks whose LOCAL state differs (one arena still held by a pending backward, one rank that has given
+    the peer transport up) must still take the same branch: the decision reads nothing but the table that
+    all ranks gathered, and "given up" wins over "busy" wins over "peer"."""
+    from fma_b200.modules import _kernels as K
+    from fma_b200.modules.moe_ep import peer_decision
+
+    E = 4
+    row = lambda busy, gone, status=0: [10, 20, 30, 40, 1024, busy, gone, status]  # noqa: E731
+    assert peer_decision([row(0, 0), row(0, 0)], E) == "peer"
+    assert peer_decision([row(0, 0), row(1, 0)], E) == "busy"  # only rank 1 is busy: both take NCCL
+    assert peer_decision([row(1, 0), row(0, 0), row(0, 0)], E) == "busy"
+    assert peer_decision([row(0, 0), row(0, 1)], E) == "unavailable"
+    assert peer_decision([row(1, 0), row(0, 1)], E) == "unavailable"
+    # the status word of the previous step: any non-zero code makes every rank raise, naming rank and code
+    K.raise_for_device_status([0, 0], "test")
+    with pytest.raises(RuntimeError, match=r"rank 1: 0x7002"):
+        K.raise_for_device_status([0, 0x7002], "test")

@@ -1,7 +1,10 @@
 """Expert-parallel MoE on 2 GPUs against the single-GPU layer holding all experts, over both
 transports: copy-engine pushes into peer-mapped arenas, and NCCL all-to-all.  Skipped on a box with
-one GPU."""
+one GPU.  FMA_B200_TEST_PEER_FUSED=1 adds the variant whose GEMM epilogues store straight into the other
+rank's arena; its store path is covered on one GPU by
+test_gpu_gemm.py::test_bf16_peer_store_epilogue_into_local_buffers."""
 
+import os
 import socket
 import sys
 from pathlib import Path
@@ -54,7 +57,8 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
 
         shard = fma_b200.shard_expert_state_dict(full.state_dict(), rank, world)
         results = {}
-        for case in ("peer", "nccl", "peer fused"):
+        cases = ("peer", "nccl") + (("peer fused",) if os.environ.get("FMA_B200_TEST_PEER_FUSED") == "1" else ())
+        for case in cases:
             # "peer fused": the down projection and the dgrad store their tiles straight into the senders' arenas
             transport = case.split()[0]
             ep = fma_b200.ExpertParallelMoE(E, k, H, I, fma_b200.swiglu_packed, True, False, 0.02, overlap_chunks=3,
@@ -100,7 +104,7 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
             elif case == "peer fused":
                 ep.close_peer_transport()
         # every variant moves the same rows into the same layouts: identical results
-        for case in ("peer", "peer fused"):
+        for case in cases:
             for a, b in zip(results[case], results["nccl"]):
                 assert torch.equal(a, b), case
         from fma_b200 import _native

@@ -181,3 +181,54 @@ def test_f32_forward_dgrad_wgrad(counts, OUT, IN):
             assert rel_l2(to_np(dX[s:t]), dY[s:t].double() @ W[e].double()) <= 1e-5 or cnt[e] == 0
         want = dY[s:t].double().T @ X[s:t].double()
         assert rel_l2(to_np(dW[e]), want) <= 1e-5
+
+
+@pytest.mark.parametrize("counts,OUT,IN", [([256, 512], 512, 128), ([5, 0, 300, 129, 700], 520, 136),
+                                           ([1000, 3, 0, 0, 77, 640], 264, 200), ([200] * 16, 1024, 512)])
+def test_bf16_peer_store_epilogue_into_local_buffers(counts, OUT, IN):
+    """The GEMMs that store every 128-row output tile at an address from a table (the expert-parallel
+    return path) with a table that points into LOCAL memory: tiles in permuted order inside one buffer,
+    every fifth tile in a second buffer.  The bits must equal the ordinary forward / dgrad.  Covers ragged
+    counts, empty experts and widths that are not multiples of 64."""
+    from fma_b200.modules import _kernels as K
+
+    E = len(counts)
+    maps, _ = _layer_maps(counts, E, 256)
+    off, cnt = _segments(maps)
+    rows = maps.rows_cap
+    n_tiles = rows // 128
+    used_tiles = off[-1] // 128
+    X = torch.zeros(rows, IN, dtype=torch.bfloat16)
+    dY = torch.zeros(rows, OUT, dtype=torch.bfloat16)
+    for e in range(E):
+        X[off[e] : off[e] + cnt[e]] = randn((cnt[e], IN), torch.bfloat16, 10 + e)
+        dY[off[e] : off[e] + cnt[e]] = randn((cnt[e], OUT), torch.bfloat16, 50 + e)
+    W = randn((E, OUT, IN), torch.bfloat16, 99, 0.1)
+    Xd, dYd, Wd = X.to(DEV), dY.to(DEV), W.to(DEV)
+    perm = torch.randperm(n_tiles, generator=torch.Generator().manual_seed(4)).tolist()
+    for kind, width in (("forward", OUT), ("dgrad", IN)):
+        ref = K.gemm_forward(Xd, Wd, maps.mtile_expert, 256) if kind == "forward" else \
+            K.gemm_dgrad(dYd, Wd, maps.mtile_expert, 256)
+        main = torch.full((n_tiles * 128, width), 7.0, dtype=torch.bfloat16, device=DEV)
+        side = torch.full((n_tiles * 128, width), 7.0, dtype=torch.bfloat16, device=DEV)
+        table = torch.empty(n_tiles, dtype=torch.int64)
+        where = []
+        for t in range(n_tiles):
+            buf = side if t % 5 == 4 else main
+            table[t] = buf.data_ptr() + perm[t] * 128 * width * 2
+            where.append((buf, perm[t]))
+        table_d = table.to(DEV)
+        if kind == "forward":
+            K.gemm_forward_peer(Xd, Wd, table_d, maps.mtile_expert, 256)
+        else:
+            K.gemm_dgrad_peer(dYd, Wd, table_d, maps.mtile_expert, 256)
+        check_device_status()
+        written = {id(main): set(), id(side): set()}
+        for t in range(used_tiles):
+            buf, slot = where[t]
+            assert torch.equal(buf[slot * 128 : (slot + 1) * 128], ref[t * 128 : (t + 1) * 128]), (kind, t)
+            written[id(buf)].add(slot)
+        for buf in (main, side):  # nothing else was touched
+            for slot in range(n_tiles):
+                if slot not in written[id(buf)]:
+                    assert torch.all(buf[slot * 128 : (slot + 1) * 128] == 7.0), (kind, slot)
