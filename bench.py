@@ -378,6 +378,23 @@ def measure_count(peaks: dict, steps: int, warmup: int, variants=(0,), big: bool
             ms = float(np.median(times))
             gbs = (n * 4 + E * 4) / ms / 1e6
             results[f"{dist_name}/variant{variant}"] = {"ms": ms, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]}
+        if dist_name == "uniform":
+            # Floor of this measurement: a library reduction that only reads the same 64 MB (torch.sum), and a
+            # kernel that does nothing, both timed the same way (events around one launch behind a busy GPU).
+            for label, fn in (("read_only_sum", lambda i: copies[i % n_copies].sum()),
+                              ("empty_launch", lambda i: torch.cuda._sleep(1))):
+                times = []
+                for i in range(warmup + steps):
+                    torch.cuda._sleep(400_000)
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    fn(i)
+                    b.record()
+                    torch.cuda.synchronize()
+                    if i >= warmup:
+                        times.append(a.elapsed_time(b))
+                ms = float(np.median(times))
+                results[f"floor/{label}"] = {"ms": ms, "gbs": (n * 4) / ms / 1e6 if label == "read_only_sum" else None}
         del copies
     if big:
         # streaming rate on an input 16x larger (1 GiB of ids), default variant: shows the size-independent part
@@ -515,7 +532,96 @@ def extra_blocks(device: torch.device, peaks: dict, peaks_kind: str, steps: int 
         del layer, x, dy
         torch.cuda.empty_cache()
     results, _ = measure_count(peaks, 20, 5, variants=(0,), big=False)
-    out["count_c2"] = {"unit": "GB/s", "uniform": results["uniform/variant0"], "zipf1.1": results["zipf1.1/variant0"]}
+    out["count_c2"] = {"unit": "GB/s", "uniform": results["uniform/variant0"], "zipf1.1": results["zipf1.1/variant0"],
+                       "floor": {k.split("/")[1]: v for k, v in results.items() if k.startswith("floor/")}}
+    return out
+
+
+def _synthetic_counts(cfg: dict) -> list[int]:
+    """Rows per expert for the GEMM comparison: R/E each under the uniform router; Zipf(1.0) loads, capped at T rows
+    per expert (an expert cannot receive a token twice), for the skewed workload."""
+    T, E, k = cfg["T"], cfg["E"], cfg["k"]
+    R = T * k
+    if cfg["router"] != "zipf":
+        return [R // E] * E
+    p = 1.0 / np.arange(1, E + 1)
+    want = np.minimum(R * p / p.sum(), T)
+    counts = np.maximum(1, np.floor(want * (R / want.sum()))).astype(np.int64)
+    counts = np.minimum(counts, T)
+    return [int(c) for c in counts]
+
+
+def reference_gpu_block(device: torch.device, names=("ep_c5",), steps: int = 5) -> dict:
+    """The six grouped GEMMs of a layer step (two forward, two dgrad, two wgrad; plain epilogues) through this
+    library's entry points and through the reference project's own CUDA kernel (its CUTLASS grouped GEMM, built
+    unmodified by baseline/build_reference_gemm.py, called through its stock entry point on its own unpadded
+    layout), on the same GPU, same row counts, same shapes.  TFLOP/s over the token rows; ratio = ours / reference."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_gemm
+    from fma_b200.modules import _kernels as K
+
+    ok, why = reference_gemm.available()
+    if ok and torch.cuda.device_count() != 1:
+        ok, why = False, "the reference kernel is run by single-GPU jobs only"
+    if not ok:
+        return {"unavailable": why}
+    try:
+        reference_gemm.load()
+    except Exception as e:  # missing symbol, other torch build, ...
+        return {"unavailable": f"cannot load the reference kernel: {e}"[:200]}
+
+    def timed(fn) -> float:
+        for _ in range(2):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    out = {"kind": "reference CUDA kernel (CUTLASS sm100 grouped GEMM, 256x256x64 2-SM tiles), stock entry point",
+           "unit": "TFLOP/s", "steps": steps}
+    u32 = lambda v: torch.tensor(v, device=device, dtype=torch.uint32)  # noqa: E731
+    for name in names:
+        cfg = WORKLOADS[name]
+        E, H, I = cfg["E"], cfg["H"], cfg["I"]
+        counts = _synthetic_counts(cfg)
+        rows = sum(counts)
+        sel = torch.repeat_interleave(torch.arange(E), torch.tensor(counts)).view(-1, 1).to(device)
+        maps = K.moe_sort(sel, E)
+        M = u32(counts)
+        res = {}
+        tot_ours = tot_ref = 0.0
+        # (label, OUT, IN) of the expert linear whose three GEMMs are timed
+        for label, OUT, IN in (("c_fc", 2 * I, H), ("c_proj", H, I)):
+            W = torch.randn(E, OUT, IN, device=device, dtype=torch.bfloat16) * 0.02
+            Nn, Kk = u32([OUT] * E), u32([IN] * E)
+            x_plain = torch.randn(rows, IN, device=device, dtype=torch.bfloat16)
+            dy_plain = torch.randn(rows, OUT, device=device, dtype=torch.bfloat16)
+            X = torch.randn(maps.rows_cap, IN, device=device, dtype=torch.bfloat16)
+            dY = torch.randn(maps.rows_cap, OUT, device=device, dtype=torch.bfloat16)
+            flops = 2.0 * rows * OUT * IN
+            cases = {
+                "forward": (lambda: K.gemm_forward(X, W, maps.mtile_expert),
+                            lambda: reference_gemm.grouped_gemm(x_plain, W, M, Nn, Kk, (rows, OUT), False, True)),
+                "dgrad": (lambda: K.gemm_dgrad(dY, W, maps.mtile_expert),
+                          lambda: reference_gemm.grouped_gemm(dy_plain, W, M, Kk, Nn, (rows, IN), False, False)),
+                "wgrad": (lambda: K.gemm_wgrad(dY, X, E, maps.pad_offsets),
+                          lambda: reference_gemm.grouped_gemm(dy_plain, x_plain, Nn, Kk, M, (E, OUT, IN), True, False)),
+            }
+            for kind, (ours, ref) in cases.items():
+                ms_o, ms_r = timed(ours), timed(ref)
+                tot_ours += ms_o
+                tot_ref += ms_r
+                res[f"{label}.{kind}"] = {"ours": flops / ms_o / 1e9, "reference": flops / ms_r / 1e9,
+                                          "ratio": ms_r / ms_o}
+            del W, x_plain, dy_plain, X, dY
+            torch.cuda.empty_cache()
+        res["all_six"] = {"ours_ms": tot_ours, "reference_ms": tot_ref, "ratio": tot_ref / tot_ours}
+        out[name] = res
     return out
 
 
@@ -571,7 +677,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="ep_c5", choices=list(WORKLOADS) + ["count_c2"])
+    ap.add_argument("--workload", default="ep_c5", choices=list(WORKLOADS) + ["count_c2", "gemm_vs_reference"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override T (for quick runs and profiler captures)")
     ap.add_argument("--ep-chunks", type=int, default=6, help="expert chunks whose exchanges overlap the GEMMs (N > 1)")
@@ -601,6 +707,14 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.tokens else args.warmup
     peaks, peaks_kind = load_peaks()
 
+    if args.workload == "gemm_vs_reference":
+        # the six grouped GEMMs of every bf16 configuration against the reference project's own CUDA kernel
+        import fma_b200  # noqa: F401
+
+        torch.cuda.set_device(0)
+        block = reference_gpu_block(torch.device("cuda:0"), ("ep_c5", "finegrained_c4", "mixtral_c3"), args.steps)
+        print(json.dumps({"metric": "grouped_gemm_tflops_vs_reference_kernel", "n_gpus": 1, "reference_gpu": block}), flush=True)
+        return
     if args.workload == "count_c2":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "count_c2 reports its CPU baseline inline"}))
@@ -812,6 +926,7 @@ def main() -> None:
         del layer, x, dy
         torch.cuda.empty_cache()
         line["extra"] = extra_blocks(device, peaks, peaks_kind)
+        line["reference_gpu"] = reference_gpu_block(device)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -121,6 +122,60 @@ struct Elem<__nv_bfloat16> {
     }
     __device__ static __forceinline__ float round(float x) { return round_bf16(x); }
 };
+
+template <>
+struct Elem<__half> {
+    static constexpr int kPerVec = 8;
+    __device__ static __forceinline__ void unpack(const uint4& v, float* f) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = p.x;
+            f[2 * i + 1] = p.y;
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float* f) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+};
+
+// float <-> one element of the three supported types
+template <typename T>
+__device__ __forceinline__ float elem_to_float(T v);
+template <>
+__device__ __forceinline__ float elem_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float elem_to_float<__half>(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T float_to_elem(float v);
+template <>
+__device__ __forceinline__ float float_to_elem<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 float_to_elem<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half float_to_elem<__half>(float v) { return __float2half_rn(v); }
+
+// Runs `body` (a generic lambda taking a value of the element type) for a dtype code; false for an unknown code.
+template <typename F>
+inline bool dispatch_dtype(int32_t dtype, F&& body) {
+    if (dtype == FMA_B200_F32) body(float{});
+    else if (dtype == FMA_B200_BF16) body(__nv_bfloat16{});
+    else if (dtype == FMA_B200_F16) body(__half{});
+    else return false;
+    return true;
+}
+inline bool known_dtype(int32_t dtype) { return dtype == FMA_B200_F32 || dtype == FMA_B200_BF16 || dtype == FMA_B200_F16; }
+inline int elems_per_16_bytes(int32_t dtype) { return dtype == FMA_B200_F32 ? 4 : 8; }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -6,28 +6,28 @@
 
 namespace fmab {
 int tc_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-               const int32_t* mtile_expert, cudaStream_t s);
+               const int32_t* mtile_expert, bool f16, cudaStream_t s);
 int tc_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                      const int32_t* mtile_expert, cudaStream_t s);
+                      const int32_t* mtile_expert, bool f16, cudaStream_t s);
 int tc_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-             const int32_t* mtile_expert, bool swiglu, cudaStream_t s);
+             const int32_t* mtile_expert, bool swiglu, bool f16, cudaStream_t s);
 int tc_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
-             const int32_t* seg_offsets, int n_seg, cudaStream_t s);
+             const int32_t* seg_offsets, int n_seg, bool f16, cudaStream_t s);
 int tc_general(const void* A, const void* B, void* D, const uint32_t* M, const uint32_t* N, const uint32_t* K,
                int n_groups, bool a_t, bool b_t, void* workspace, int64_t workspace_bytes, cudaStream_t s);
 int64_t tc_general_workspace_bytes(int n_groups, int64_t total_mtiles);
 int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-                const int32_t* mtile_expert, bool narrow, cudaStream_t s);
+                const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s);
 int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                       const int32_t* mtile_expert, bool narrow, cudaStream_t s);
+                       const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s);
 int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* mtile_expert, bool swiglu, bool narrow, cudaStream_t s);
+              const int32_t* mtile_expert, bool swiglu, bool narrow, bool f16, cudaStream_t s);
 int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* seg_offsets, int n_seg, cudaStream_t s);
+              const int32_t* seg_offsets, int n_seg, bool f16, cudaStream_t s);
 int tc2_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
-                     const int32_t* mtile_expert, cudaStream_t s);
+                     const int32_t* mtile_expert, bool f16, cudaStream_t s);
 int tc2_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
-                   const int32_t* mtile_expert, cudaStream_t s);
+                   const int32_t* mtile_expert, bool f16, cudaStream_t s);
 int simt_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
                  const int32_t* mtile_expert, cudaStream_t s);
 int simt_dgrad(const void* dY, const void* W, void* dX, int64_t rows_cap, int E, int OUT, int IN,
@@ -35,20 +35,25 @@ int simt_dgrad(const void* dY, const void* W, void* dX, int64_t rows_cap, int E,
 int simt_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
                const int32_t* seg_offsets, int n_seg, cudaStream_t s);
 
-// CTA-pair kernels (cta_group::2) are used when the grouped rows are aligned to 256; FMA_B200_GEMM_PAIRS=0
-// forces the single-CTA kernels (a measurement knob).
-static bool use_pairs(int32_t row_align) {
-    static int enabled = -1;
-    if (enabled < 0) {
+// CTA-pair kernels (cta_group::2) are used when the grouped rows are aligned to 256.  Measurement knob
+// FMA_B200_GEMM_PAIRS: 0 forces the single-CTA kernels everywhere, 1 keeps the two SwiGLU-epilogue GEMMs on
+// the single-CTA kernel (its two accumulators belong to different tiles, so a long epilogue overlaps the next
+// main loop), anything else (the default) runs all five layer GEMMs on pairs.
+static int pairs_mode() {
+    static int mode = -1;
+    if (mode < 0) {
         const char* env = getenv("FMA_B200_GEMM_PAIRS");
-        enabled = (env != nullptr && atoi(env) == 0) ? 0 : 1;
+        mode = (env == nullptr) ? 2 : atoi(env);
+        if (mode < 0 || mode > 2) mode = 2;
     }
-    return enabled == 1 && row_align > 0 && row_align % 256 == 0;
+    return mode;
 }
+static bool use_pairs(int32_t row_align) { return pairs_mode() >= 1 && row_align > 0 && row_align % 256 == 0; }
 
 // Measurement knob FMA_B200_GEMM_NARROW (bit mask, default 0 = off): the pair kernels with 256x256 tiles whose
-// two tensor-memory halves belong to consecutive tiles.  Bit 0: the two SwiGLU-epilogue GEMMs (which then run
-// on CTA pairs), bit 1: the plain forward GEMM, bit 2: the plain dgrad GEMM.
+// two tensor-memory halves belong to consecutive tiles.  Bit 0: the two SwiGLU-epilogue GEMMs, bit 1: the
+// plain forward GEMM, bit 2: the plain dgrad GEMM.  Measured slower than the 256x512 tiles at every
+// benchmarked shape except the plain forward GEMM with K = 768.
 static int narrow_mask() {
     static int v = -1;
     if (v < 0) {
@@ -58,13 +63,10 @@ static int narrow_mask() {
     return v;
 }
 
-static bool pairs_for_fused_epilogues() {
-    const char* env = getenv("FMA_B200_GEMM_PAIRS");
-    return (env != nullptr && atoi(env) == 2) || (narrow_mask() & 1);
-}
+static bool pairs_for_fused_epilogues() { return pairs_mode() == 2 || (narrow_mask() & 1); }
 
 static int check_layer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN) {
-    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    FMAB_REQUIRE(known_dtype(dtype), FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
     FMAB_REQUIRE(rows_cap >= 0 && rows_cap % 128 == 0 && rows_cap < (1LL << 31), FMA_B200_ERR_BAD_ARG,
                  "rows_cap=%lld must be a multiple of 128 below 2^31", (long long)rows_cap);
     FMAB_REQUIRE(E >= 1 && E <= 1024, FMA_B200_ERR_BAD_ARG, "E=%d not in [1,1024]", E);
@@ -85,9 +87,10 @@ int fma_b200_moe_gemm_forward(const void* X, const void* W, void* Y, int32_t dty
     FMAB_REQUIRE(X && W && Y && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(X) && aligned16(W) && aligned16(Y), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_BF16 && use_pairs(row_align))
-        return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, (narrow_mask() & 2) != 0, s);
-    if (dtype == FMA_B200_BF16) return tc_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
+    const bool f16 = dtype == FMA_B200_F16;
+    if (dtype != FMA_B200_F32 && use_pairs(row_align))
+        return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, (narrow_mask() & 2) != 0, f16, s);
+    if (dtype != FMA_B200_F32) return tc_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, f16, s);
     return simt_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
 }
 
@@ -99,9 +102,10 @@ int fma_b200_moe_gemm_dgrad(const void* dY, const void* W, void* dX, int32_t dty
     FMAB_REQUIRE(dY && W && dX && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(dX), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_BF16 && use_pairs(row_align))
-        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, (narrow_mask() & 4) != 0, s);
-    if (dtype == FMA_B200_BF16) return tc_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, s);
+    const bool f16 = dtype == FMA_B200_F16;
+    if (dtype != FMA_B200_F32 && use_pairs(row_align))
+        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, (narrow_mask() & 4) != 0, f16, s);
+    if (dtype != FMA_B200_F32) return tc_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, f16, s);
     return simt_dgrad(dY, W, dX, rows_cap, E, OUT, IN, mtile_expert, s);
 }
 
@@ -114,8 +118,9 @@ int fma_b200_moe_gemm_wgrad(const void* dY, const void* X, void* dW, int32_t dty
     FMAB_REQUIRE(rows_cap > 0 && dY && X, FMA_B200_ERR_BAD_ARG, "wgrad needs non-empty dY and X buffers");
     FMAB_REQUIRE(aligned16(dY) && aligned16(X) && aligned16(dW), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_BF16 && use_pairs(256)) return tc2_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, s);
-    if (dtype == FMA_B200_BF16) return tc_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, s);
+    const bool f16 = dtype == FMA_B200_F16;
+    if (dtype != FMA_B200_F32 && use_pairs(256)) return tc2_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, f16, s);
+    if (dtype != FMA_B200_F32) return tc_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, f16, s);
     return simt_wgrad(dY, X, dW, rows_cap, E, OUT, IN, seg_offsets, n_seg, s);
 }
 
@@ -123,42 +128,43 @@ int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, vo
                                      int64_t rows_cap, int32_t E, int32_t I, int32_t IN, const int32_t* mtile_expert,
                                      int32_t row_align, void* stream) {
     using namespace fmab;
-    FMAB_REQUIRE(dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED,
-                 "the SwiGLU-fused up projection exists for bf16 only; run forward + swiglu_forward for f32");
+    FMAB_REQUIRE(dtype == FMA_B200_BF16 || dtype == FMA_B200_F16, FMA_B200_ERR_UNSUPPORTED,
+                 "the SwiGLU-fused up projection exists for the 16-bit types only; run forward + swiglu_forward for f32");
+    const bool f16 = dtype == FMA_B200_F16;
     FMAB_REQUIRE(I >= 8 && I % 8 == 0 && I < (1 << 29), FMA_B200_ERR_BAD_ARG, "I=%d must be a positive multiple of 8", I);
     if (int rc = check_layer_gemm(dtype, rows_cap, E, 2 * I, IN)) return rc;
     if (rows_cap == 0) return FMA_B200_OK;
     FMAB_REQUIRE(X && W && act && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(X) && aligned16(W) && aligned16(act) && aligned16(pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
-    // The SwiGLU epilogues are long; they run on the single-CTA kernel, whose two accumulators belong to
-    // different tiles so that an epilogue overlaps the next tile's main loop (FMA_B200_GEMM_PAIRS=2 forces pairs).
     if (use_pairs(row_align) && pairs_for_fused_epilogues())
-        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, (narrow_mask() & 1) != 0,
+        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, (narrow_mask() & 1) != 0, f16,
                                   static_cast<cudaStream_t>(stream));
-    return tc_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, static_cast<cudaStream_t>(stream));
+    return tc_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, f16, static_cast<cudaStream_t>(stream));
 }
 
 int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pre, void* d_pre, int32_t dtype,
                                    int64_t rows_cap, int32_t E, int32_t OUT, int32_t I, const int32_t* mtile_expert,
                                    int32_t row_align, void* stream) {
     using namespace fmab;
-    FMAB_REQUIRE(dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED,
-                 "the SwiGLU-fused dgrad exists for bf16 only; run dgrad + swiglu_backward for f32");
+    FMAB_REQUIRE(dtype == FMA_B200_BF16 || dtype == FMA_B200_F16, FMA_B200_ERR_UNSUPPORTED,
+                 "the SwiGLU-fused dgrad exists for the 16-bit types only; run dgrad + swiglu_backward for f32");
+    const bool f16 = dtype == FMA_B200_F16;
     if (int rc = check_layer_gemm(dtype, rows_cap, E, OUT, I)) return rc;
     if (rows_cap == 0) return FMA_B200_OK;
     FMAB_REQUIRE(dY && W && pre && d_pre && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(pre) && aligned16(d_pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
     if (use_pairs(row_align) && pairs_for_fused_epilogues())
-        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, (narrow_mask() & 1) != 0,
+        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, (narrow_mask() & 1) != 0, f16,
                          static_cast<cudaStream_t>(stream));
-    return tc_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, static_cast<cudaStream_t>(stream));
+    return tc_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, f16, static_cast<cudaStream_t>(stream));
 }
 
 static int check_peer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN, int32_t row_align) {
     using namespace fmab;
-    FMAB_REQUIRE(dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "the peer-store GEMMs exist for bf16 only");
+    FMAB_REQUIRE(dtype == FMA_B200_BF16 || dtype == FMA_B200_F16, FMA_B200_ERR_UNSUPPORTED,
+                 "the peer-store GEMMs exist for the 16-bit types only");
     FMAB_REQUIRE(row_align > 0 && row_align % 256 == 0, FMA_B200_ERR_UNSUPPORTED,
                  "the peer-store GEMMs run on CTA pairs: row_align=%d must be a multiple of 256", row_align);
     return check_layer_gemm(dtype, rows_cap, E, OUT, IN);
@@ -172,7 +178,8 @@ int fma_b200_moe_gemm_forward_peer(const void* X, const void* W, const uint64_t*
     if (rows_cap == 0) return FMA_B200_OK;
     FMAB_REQUIRE(X && W && dst_table && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(X) && aligned16(W), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
-    return tc2_forward_peer(X, W, dst_table, rows_cap, E, OUT, IN, mtile_expert, static_cast<cudaStream_t>(stream));
+    return tc2_forward_peer(X, W, dst_table, rows_cap, E, OUT, IN, mtile_expert, dtype == FMA_B200_F16,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int fma_b200_moe_gemm_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int32_t dtype,
@@ -183,7 +190,8 @@ int fma_b200_moe_gemm_dgrad_peer(const void* dY, const void* W, const uint64_t* 
     if (rows_cap == 0) return FMA_B200_OK;
     FMAB_REQUIRE(dY && W && dst_table && mtile_expert, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     FMAB_REQUIRE(aligned16(dY) && aligned16(W), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
-    return tc2_dgrad_peer(dY, W, dst_table, rows_cap, E, OUT, IN, mtile_expert, static_cast<cudaStream_t>(stream));
+    return tc2_dgrad_peer(dY, W, dst_table, rows_cap, E, OUT, IN, mtile_expert, dtype == FMA_B200_F16,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int64_t fma_b200_grouped_gemm_workspace_bytes(int32_t n_groups, int64_t total_mtiles) {

@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_instr_desc<A_MN, B_MN>();
+            const uint32_t idesc = with_operand_format(make_instr_desc<A_MN, B_MN>(), p.f16 != 0);
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
@@ -334,6 +334,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
         constexpr int kColSplit = EPI_WARPS / 4;  // 1: every warp stores all columns of its rows; 2: half each
         const int half = (warp - 2) >> 2;         // which part of the tile's columns this warp stores
         const int row_in_tile = quad * 32 + lane;
+        const bool f16 = p.f16 != 0;
         int buf = 0;
         uint32_t acc_phase = 0;
         int sslot = 0;
@@ -378,7 +379,7 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = 0.f;
                     }
-                    if (row_ok) store_row32_bf16(drow + c * 32, v, cols_left);
+                    if (row_ok) store_row32(drow + c * 32, v, cols_left, f16);
                 }
             } else if (EPI == EPI_SWIGLU_FWD) {
                 // accumulator columns [0,128) = up, [128,256) = gate, for act columns n0..n0+127
@@ -394,16 +395,16 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
                     tc_load_32(taddr + BN / 2 + c * 32, g);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        u[i] = round_bf16(u[i]);
-                        g[i] = round_bf16(g[i]);
+                        u[i] = round16(u[i], f16);
+                        g[i] = round16(g[i], f16);
                     }
                     if (row_ok && prow) {
-                        store_row32_bf16(prow + c * 32, u, cols_left);
-                        store_row32_bf16(prow + p.inter + c * 32, g, cols_left);
+                        store_row32(prow + c * 32, u, cols_left, f16);
+                        store_row32(prow + p.inter + c * 32, g, cols_left, f16);
                     }
 #pragma unroll
                     for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped_fast(g[i]);
-                    if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
+                    if (row_ok) store_row32(arow + c * 32, u, cols_left, f16);
                 }
             } else {
                 // d_act tile -> d_up, d_gate using the saved pre-activations.  The up/gate values of the
@@ -431,21 +432,21 @@ __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1) gemm_tc_kernel(const _
                     tc_load_32(taddr + c * 32, da);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        Elem<__nv_bfloat16>::unpack(nu[q], u + q * 8);
-                        Elem<__nv_bfloat16>::unpack(ng[q], g + q * 8);
+                        unpack8(nu[q], u + q * 8, f16);
+                        unpack8(ng[q], g + q * 8, f16);
                     }
                     if (c + 1 < c_end) fetch(c + 1);
                     if (row_ok) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const float d = round_bf16(da[i]);
+                            const float d = round16(da[i], f16);
                             const float s = sigmoid_clamped_fast(g[i]);
                             const float silu = g[i] * s;
                             da[i] = d * silu;                           // d_up
                             g[i] = d * u[i] * (s + silu * (1.f - s));   // d_gate
                         }
-                        store_row32_bf16(drow + c * 32, da, cols_left);
-                        store_row32_bf16(drow + p.inter + c * 32, g, cols_left);
+                        store_row32(drow + c * 32, da, cols_left, f16);
+                        store_row32(drow + p.inter + c * 32, g, cols_left, f16);
                     }
                 }
             }
@@ -525,11 +526,12 @@ static int fill_common(GemmParams& p) {
 }
 
 int tc_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-               const int32_t* mtile_expert, cudaStream_t s) {
+               const int32_t* mtile_expert, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, BN)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, BN, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.d = static_cast<__nv_bfloat16*>(Y);
@@ -544,11 +546,12 @@ int tc_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, i
 }
 
 int tc_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                      const int32_t* mtile_expert, cudaStream_t s) {
+                      const int32_t* mtile_expert, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * 2 * I, IN, BK, BN / 2)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * 2 * I, IN, BK, BN / 2, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.d = static_cast<__nv_bfloat16*>(act);
@@ -565,12 +568,13 @@ int tc_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_
 }
 
 int tc_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-             const int32_t* mtile_expert, bool swiglu, cudaStream_t s) {
+             const int32_t* mtile_expert, bool swiglu, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM, f16)) return rc;
     // W[e] is [OUT, IN] row-major = the [K, N] operand with N contiguous: MN-major B, boxes of 64 columns x BK rows
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.d = static_cast<__nv_bfloat16*>(dX);
@@ -588,12 +592,12 @@ int tc_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t r
 }
 
 int tc_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
-             const int32_t* seg_offsets, int n_seg, cudaStream_t s) {
+             const int32_t* seg_offsets, int n_seg, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_common(p)) return rc;
     // both operands are [tokens, features] row-major: the token (reduction) index is the outer dimension
-    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, 64, BK)) return rc;
-    if (int rc = encode_2d(&p.map_b, X, IN, rows_cap, IN, 64, BK)) return rc;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, 64, BK, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, X, IN, rows_cap, IN, 64, BK, f16)) return rc;
     p.mode = MODE_WGRAD;
     p.seg_offsets = seg_offsets;
     p.n_seg = n_seg;

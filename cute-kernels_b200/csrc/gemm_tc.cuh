@@ -78,12 +78,10 @@ struct GemmParams {
     int32_t dynamic_tiles;        // 1: tiles drawn from the global counter; 0: tile = blockIdx.x + i * gridDim.x
     int32_t pair_skew;            // CTA-pair kernel: k-blocks by which accumulator half 1 trails half 0
     const uint64_t* mtile_dst;    // EPI_PLAIN_PEER: byte address of output row 0 of every 128-row tile (pitch ldd)
-    // CTA-pair kernel, epilogues that leave through shared memory and TMA stores: 3-D maps {columns, rows,
-    // group} with 64-column x 32-row boxes of the output (map_d) and, for the SwiGLU epilogues, of the second
-    // output / the saved pre-activations (map_d2).  Rows mode uses group coordinate 0.
+    // CTA-pair kernel, plain epilogue: output as a 3-D map {columns, rows, group} with boxes of 32 columns x
+    // 32 rows for TMA stores; group coordinate 0 in rows mode.
     CUtensorMap map_d;
-    CUtensorMap map_d2;
-    int32_t tma_store;            // 1: the epilogue stores through map_d (and map_d2)
+    int32_t f16;  // 1: operands and outputs are IEEE half instead of bfloat16 (same kernels, same 16-bit layouts)
 };
 
 // ---------------------------------------------------------------------------
@@ -135,9 +133,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
-// TMA store of a 64-column x 32-row box from shared memory (128-byte swizzle) to coordinates {c0, c1, c2}.
-// Out-of-range parts of the box are not written.  Completion is tracked by the issuing thread's bulk
-// async-group: commit, then wait (".read": the source has been read and may be overwritten).
+// TMA store of one box of a 3-D map from shared memory to coordinates {c0, c1, c2}.  Out-of-range parts of
+// the box are not written.  Completion is tracked by the issuing thread's bulk async-groups: commit, then
+// wait (".read": the source has been read and may be overwritten; "but one": all groups except the latest).
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
@@ -145,6 +143,7 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Makes this thread's shared-memory writes visible to the async proxy (TMA) before a store is issued.
 __device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -190,6 +189,21 @@ __device__ __forceinline__ void tc_load_32(uint32_t taddr, float* v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same load without the wait, so that several can be in flight; tc_load_wait() makes all of them valid.
+__device__ __forceinline__ void tc_load_32_issue(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile.
 //   K-major : rows of 64 bf16 (128 B); 8-row groups 1024 B apart (stride byte offset).
 //   MN-major: rows of 64 MN elements (128 B) per k; 8-k groups 1024 B apart (stride byte offset);
@@ -210,10 +224,15 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 template <bool MN_MAJOR>
 __device__ __forceinline__ constexpr uint32_t desc_k_step() { return MN_MAJOR ? UMMA_K * 128 : UMMA_K * 2; }
 
+// A/B format field of the kind::f16 instruction descriptor: 1 = bfloat16, 0 = IEEE half.
+__device__ __forceinline__ uint32_t with_operand_format(uint32_t idesc_bf16, bool f16) {
+    return f16 ? (idesc_bf16 & ~((7u << 7) | (7u << 10))) : idesc_bf16;
+}
+
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ constexpr uint32_t make_instr_desc() {
     return (1u << 4)                      // accumulator format: fp32
-           | (1u << 7)                    // A format: bf16
+           | (1u << 7)                    // A format: bf16 (see with_operand_format)
            | (1u << 10)                   // B format: bf16
            | ((A_MN ? 1u : 0u) << 15)     // A major
            | ((B_MN ? 1u : 0u) << 16)     // B major
@@ -223,19 +242,31 @@ __device__ __forceinline__ constexpr uint32_t make_instr_desc() {
 
 
 // ---------------------------------------------------------------------------
-// epilogue helpers: one thread owns one output row, 32 columns at a time
+// epilogue helpers
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float* v, int cols_left) {
+// The kernels handle bfloat16 and IEEE half with the same code: both are 16-bit elements, the tensor cores
+// take either (a field of the instruction descriptor), and only the conversions at the edges differ.  `f16` is
+// a kernel parameter, uniform over the launch.
+__device__ __forceinline__ uint4 pack8(const float* f, bool f16) {
+    return f16 ? Elem<__half>::pack(f) : Elem<__nv_bfloat16>::pack(f);
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f, bool f16) {
+    if (f16) Elem<__half>::unpack(v, f); else Elem<__nv_bfloat16>::unpack(v, f);
+}
+__device__ __forceinline__ float round16(float x, bool f16) { return f16 ? Elem<__half>::round(x) : round_bf16(x); }
+
+// one thread owns one output row, 32 columns at a time
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float* v, int cols_left, bool f16) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        if (q * 8 < cols_left) st_global_16(dst + q * 8, Elem<__nv_bfloat16>::pack(v + q * 8));
+        if (q * 8 < cols_left) st_global_16(dst + q * 8, pack8(v + q * 8, f16));
     }
 }
-__device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float* v, int cols_left) {
+__device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float* v, int cols_left, bool f16) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         if (q * 8 < cols_left) {
-            Elem<__nv_bfloat16>::unpack(ld_global_16(src + q * 8), v + q * 8);
+            unpack8(ld_global_16(src + q * 8), v + q * 8, f16);
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[q * 8 + i] = 0.f;
@@ -263,9 +294,9 @@ inline EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 2-D bf16 tensor [outer, inner] with row pitch `pitch` elements, box [box_outer, box_inner], 128-byte swizzle.
+// 2-D tensor of 16-bit elements [outer, inner] with row pitch `pitch` elements, box [box_outer, box_inner], 128-byte swizzle.
 inline int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
-                     uint32_t box_inner, uint32_t box_outer) {
+                     uint32_t box_inner, uint32_t box_outer, bool f16 = false) {
     EncodeTiledFn fn = encode_fn();
     FMAB_REQUIRE(fn != nullptr, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
     FMAB_REQUIRE(aligned16(base), FMA_B200_ERR_BAD_ARG, "GEMM operand is not 16-byte aligned");
@@ -276,17 +307,18 @@ inline int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
     const cuuint64_t strides[1] = {pitch * 2};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    const CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                          const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FMAB_REQUIRE(r == CUDA_SUCCESS, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return FMA_B200_OK;
 }
 
-// 3-D bf16 tensor {d0 (contiguous), d1, d2} with pitches in elements, boxes of box0 x box1 x 1, 128-byte swizzle:
-// the output maps of the epilogues that store with TMA.
+// 3-D tensor of 16-bit elements {d0 (contiguous), d1, d2} with pitches in elements, boxes of box0 x box1 x 1 whose rows are
+// box0 * 2 = 64 bytes wide, 64-byte swizzle: the output map of the epilogue that stores with TMA.
 inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
-                     uint64_t pitch2, uint32_t box0, uint32_t box1) {
+                     uint64_t pitch2, uint32_t box0, uint32_t box1, bool f16 = false) {
     EncodeTiledFn fn = encode_fn();
     FMAB_REQUIRE(fn != nullptr, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
     FMAB_REQUIRE(aligned16(base), FMA_B200_ERR_BAD_ARG, "GEMM output is not 16-byte aligned");
@@ -298,8 +330,9 @@ inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d
     const cuuint64_t strides[2] = {pitch1 * 2, pitch2 * 2};
     const cuuint32_t box[3] = {box0, box1, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    const CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                          const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FMAB_REQUIRE(r == CUDA_SUCCESS, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
     return FMA_B200_OK;

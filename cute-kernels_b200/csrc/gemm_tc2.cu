@@ -52,15 +52,25 @@ struct PairShape {
     static constexpr int kStageBytes = A_STAGE_BYTES + HALVES * PAIR_B_BYTES;  // 16 KB + HALVES x 16 KB
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
 };
-// The epilogues stage every 32-row x 64-column piece of the output in shared memory (a 4 KB patch per
-// epilogue warp, behind the operand ring) so that it leaves the SM as whole 128-byte row segments: one
-// thread per row storing straight from its registers makes every store instruction touch 32 different
-// 128-byte lines, and the load/store unit then needs about 12k cycles to drain a 256x512 tile, half as long
-// as the tile's main loop at K = 1536.  From the patch (128-byte swizzle, the layout TMA expects) the piece
-// goes out as ONE TMA store issued by one lane (EPI_PLAIN and the SwiGLU epilogues), or as eight fully
-// coalesced 512-byte store instructions where the destination is an arbitrary address (EPI_PLAIN_PEER).
+// Every epilogue passes its output through shared memory (a 4 KB patch per epilogue warp, behind the operand
+// ring).  Tensor memory hands out an accumulator one row per lane; storing that straight from registers makes
+// every store instruction touch 32 different 128-byte lines.  From the patch the output leaves
+//   - as TMA stores issued by one lane (plain epilogue: 32 rows x 32 columns per store, the two halves of the
+//     patch alternating), or
+//   - in "line form": store instructions that each cover four whole 128-byte row segments (the peer-store
+//     epilogue, whose destinations are arbitrary addresses, and the SwiGLU epilogues, which also do their
+//     elementwise math in that form so that `pre` is read and written as whole lines too).
 constexpr int PEER_PATCH_BYTES = 32 * 128;
 constexpr size_t PEER_PATCH_TOTAL = static_cast<size_t>(PAIR_EPI_WARPS) * PEER_PATCH_BYTES;
+
+// Address of the 16-byte piece (row, piece) of a per-warp staging patch: 32 rows x 128 bytes, pieces
+// XOR-swizzled by the row.  Both ways the epilogues touch a patch are then free of bank conflicts:
+//   row form   lane = row, one piece per access (how tensor memory hands out an accumulator: a row per lane);
+//   line form  one access covers 4 rows x 8 pieces, i.e. four whole 128-byte rows (what global memory likes):
+//              step `it` (0..7) gives lane the piece (row it*4 + lane/8, piece lane%8).
+__device__ __forceinline__ uint32_t patch_addr(uint32_t patch, int row, int piece) {
+    return patch + row * 128 + ((static_cast<uint32_t>(piece) ^ (static_cast<uint32_t>(row) & 7u)) << 4);
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -79,6 +89,14 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same arrive without release semantics.  A releasing arrive at cluster scope has to wait until every
+// global store the thread has issued is visible cluster-wide, i.e. until the epilogue's output has drained to
+// L2 - a microsecond or two per tile during which the tensor memory it frees stays blocked.  What an epilogue
+// warp hands back is tensor memory it has finished reading (tcgen05.wait::ld has returned and a
+// tcgen05.fence::before_thread_sync precedes the arrive); its global stores need no ordering with the barrier.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -351,7 +369,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
     } else if (warp == 1) {
         // ------------------------------ MMA issuer (leader CTA only) ------------------------------
         if (leader && lane == 0) {
-            constexpr uint32_t idesc = make_instr_desc_pair<A_MN, B_MN>();
+            const uint32_t idesc = with_operand_format(make_instr_desc_pair<A_MN, B_MN>(), p.f16 != 0);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_phase = 0;
@@ -469,9 +487,10 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
         // ------------------------------ epilogue (both CTAs, own 128 rows) ------------------------------
         const int quad = warp & 3;
         const int half = (warp - 2) >> 2;
-        const int row_in_tile = quad * 32 + lane;
+        const bool f16 = p.f16 != 0;
         uint32_t acc_phase = 0;
         uint32_t tile_count = 0;
+        uint32_t store_seq = 0;  // TMA stores issued by this warp: picks the half of its patch
         int sslot = 0;
         uint32_t sphase = 0;
         while (true) {
@@ -492,9 +511,30 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 decode_pair_segment(p, t, s, a_k0, b_k0, len);
                 any_k |= len > 0;
             }
-            const bool row_ok = row_in_tile < t.rows_valid;
-            const int64_t grow = t.d_row + row_in_tile;
+            const uint32_t patch = ring + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * PEER_PATCH_BYTES;
+            const int lr = lane >> 3, lp = lane & 7;  // line form: row within a 4-row step, 16-byte piece of the row
+            constexpr int kGroups = BN / 64 / 2;       // 64-column groups per warp and accumulator half
             bool alive = true;
+
+            // SwiGLU backward: the saved up / gate values of one 64-column group in line form.  They are fetched
+            // ahead of their use: for the tile's first group before the accumulator is even awaited (the main loop
+            // is still running then), for every later group while the previous one is being computed.
+            uint4 cu[8], cg[8];
+            const int64_t pre_pitch = 2 * static_cast<int64_t>(p.inter);
+            auto bwd_fetch = [&](int h, int g, int it) {
+                const int n0 = t.n0 + h * t.n_step;
+                const int left = min(t.n_step, p.n_cols - n0) - g * 64;
+                const int row = quad * 32 + it * 4 + lr;
+                const bool ok = h < HALVES && lp * 8 < left && row < t.rows_valid;
+                const __nv_bfloat16* src = p.pre + (t.d_row + row) * pre_pitch + n0 + g * 64 + lp * 8;
+                cu[it] = ok ? ld_global_16(src) : make_uint4(0, 0, 0, 0);
+                cg[it] = ok ? ld_global_16(src + p.inter) : make_uint4(0, 0, 0, 0);
+            };
+            if (EPI == EPI_SWIGLU_BWD) {
+#pragma unroll
+                for (int it = 0; it < 8; ++it) bwd_fetch(0, half * kGroups, it);
+            }
+
             for (int h = 0; h < HALVES; ++h) {
             // tensor-memory half and barrier parity of this part of the tile (see the MMA warp)
             const int hs = (HALVES == 1) ? static_cast<int>(tile_count & 1u) : h;
@@ -508,19 +548,57 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             const int n0h = t.n0 + h * t.n_step;                 // first D column of this half
             const int n_valid = min(t.n_step, p.n_cols - n0h);   // <= 0: the half carries no columns
 
-            if (EPI == EPI_PLAIN && p.tma_store) {
-                // registers -> swizzled patch -> one TMA store per 32 rows x 64 columns
-                const uint32_t patch = ring + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * PEER_PATCH_BYTES;
-                constexpr int kGroups = BN / 64 / 2;  // 64-column groups per warp and half
+            if (EPI == EPI_PLAIN) {
+                // 32 rows x 32 columns at a time: accumulator -> bf16 -> one half of the warp's patch (64-byte
+                // rows, 64-byte swizzle) -> ONE TMA store issued by lane 0.  The two halves of the patch
+                // alternate, so a store drains while the next piece is converted and written.
+                constexpr int kChunks = BN / 32 / 2;
                 const int row_c = ((p.mode == MODE_ROWS) ? static_cast<int>(t.d_row) : t.a_mn) + quad * 32;
                 const int grp_c = (p.mode == MODE_ROWS) ? 0 : t.group;
                 const bool rows_here = quad * 32 < t.rows_valid;
 #pragma unroll 1
+                for (int c = half * kChunks; c < (half + 1) * kChunks; c += 2) {
+                    const int cols_left = n_valid - c * 32;
+                    if (cols_left <= 0) break;
+                    uint32_t ra[32], rb[32];
+                    if (any_k) {  // both pieces of the pair are requested before either is awaited
+                        tc_load_32_issue(taddr + c * 32, ra);
+                        if (cols_left > 32) tc_load_32_issue(taddr + c * 32 + 32, rb);
+                        tc_load_wait();
+                    }
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        if (cols_left <= q * 32) break;
+                        const uint32_t* r = q ? rb : ra;
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = any_k ? __uint_as_float(r[i]) : 0.f;
+                        const uint32_t sub = patch + (store_seq & 1u) * (PEER_PATCH_BYTES / 2);
+                        ++store_seq;
+                        if (lane == 0) bulk_wait_read_but_one();  // the store that last used this half has read it
+                        __syncwarp();
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            st_shared_16(sub + lane * 64 + ((static_cast<uint32_t>(k) ^ ((lane >> 1) & 3u)) << 4),
+                                         pack8(v + k * 8, f16));
+                        fence_smem_to_async();
+                        __syncwarp();
+                        if (lane == 0 && rows_here) {
+                            tma_store_3d(&p.map_d, sub, n0h + (c + q) * 32, row_c, grp_c);
+                            bulk_commit();
+                        }
+                    }
+                }
+            } else if (EPI == EPI_PLAIN_PEER) {
+                // 32 rows x 64 columns at a time: accumulator -> bf16 -> patch in row form -> read back in line
+                // form -> eight store instructions of four whole 128-byte row segments each.  The 128 rows of
+                // this CTA's tile go to the address from the per-tile table (possibly another GPU's memory), same
+                // pitch; what crosses NVLink are whole 128-byte lines.
+                uint8_t* dst_tile = reinterpret_cast<uint8_t*>(__ldg(p.mtile_dst + (t.d_row >> 7)));
+#pragma unroll 1
                 for (int g = half * kGroups; g < (half + 1) * kGroups; ++g) {
                     const int cols_left = n_valid - g * 64;
                     if (cols_left <= 0) break;
-                    if (lane == 0) bulk_wait_read_all();  // the previous store has read the patch
-                    __syncwarp();
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
                         float v[32];
@@ -531,151 +609,131 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                             for (int i = 0; i < 32; ++i) v[i] = 0.f;
                         }
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint32_t piece = static_cast<uint32_t>(q * 4 + k) ^ (lane & 7);
-                            st_shared_16(patch + lane * 128 + piece * 16, Elem<__nv_bfloat16>::pack(v + k * 8));
-                        }
-                    }
-                    fence_smem_to_async();
-                    __syncwarp();
-                    if (lane == 0 && rows_here) {
-                        tma_store_3d(&p.map_d, patch, n0h + g * 64, row_c, grp_c);
-                        bulk_commit();
-                    }
-                }
-            } else if (EPI == EPI_PLAIN) {
-                __nv_bfloat16* drow = p.d + grow * p.ldd + n0h;
-                constexpr int kChunks = BN / 32 / 2;
-#pragma unroll 1
-                for (int c = half * kChunks; c < (half + 1) * kChunks; ++c) {
-                    const int cols_left = n_valid - c * 32;
-                    if (cols_left <= 0) break;
-                    float v[32];
-                    if (any_k) {
-                        tc_load_32(taddr + c * 32, v);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                    }
-                    if (row_ok) store_row32_bf16(drow + c * 32, v, cols_left);
-                }
-            } else if (EPI == EPI_PLAIN_PEER) {
-                // The 128 rows of this CTA's tile go to one destination (possibly another GPU's memory):
-                // address of row 0 from the per-tile table, same pitch.  Stores that cross NVLink should be
-                // whole 128-byte lines, so two 32-column chunks are transposed through a 4 KB patch of shared
-                // memory: lane = row when the patch is written, (4 rows x 8 pieces of 16 B) per store
-                // instruction when it is read.  Pieces are XOR-swizzled by the row so that neither phase has
-                // bank conflicts.
-                uint8_t* dst_tile = reinterpret_cast<uint8_t*>(__ldg(p.mtile_dst + (t.d_row >> 7)));
-                const uint32_t patch = ring + PAIR_STAGES * PAIR_STAGE_BYTES + (warp - 2) * PEER_PATCH_BYTES;
-                constexpr int kPairs = BN / 64 / 2;  // 64-column groups per warp and half
-#pragma unroll 1
-                for (int g = half * kPairs; g < (half + 1) * kPairs; ++g) {
-                    const int cols_left = n_valid - g * 64;
-                    if (cols_left <= 0) break;
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        float v[32];
-                        if (any_k && cols_left > q * 32) {
-                            tc_load_32(taddr + g * 64 + q * 32, v);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint4 w = Elem<__nv_bfloat16>::pack(v + k * 8);
-                            const uint32_t piece = static_cast<uint32_t>(q * 4 + k) ^ (lane & 7);
-                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 128 + piece * 16),
-                                         "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w)
-                                         : "memory");
-                        }
+                        for (int k = 0; k < 4; ++k)
+                            st_shared_16(patch_addr(patch, lane, q * 4 + k), pack8(v + k * 8, f16));
                     }
                     __syncwarp();
 #pragma unroll
                     for (int it = 0; it < 8; ++it) {
-                        const int r = it * 4 + (lane >> 3);   // row of the warp's 32
-                        const int piece = lane & 7;           // 16-byte piece of the 128-byte segment
-                        uint4 w;
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
-                                     : "r"(patch + r * 128 + ((piece ^ (r & 7)) * 16))
-                                     : "memory");
+                        const int r = it * 4 + lr;
+                        const uint4 w = ld_shared_16(patch_addr(patch, r, lp));
                         const int row = quad * 32 + r;
-                        if (row < t.rows_valid && piece * 8 < cols_left)
-                            st_global_16(dst_tile + (static_cast<int64_t>(row) * p.ldd + n0h + g * 64 + piece * 8) * 2, w);
+                        if (row < t.rows_valid && lp * 8 < cols_left)
+                            st_global_16(dst_tile + (static_cast<int64_t>(row) * p.ldd + n0h + g * 64 + lp * 8) * 2, w);
                     }
                     __syncwarp();
                 }
             } else if (EPI == EPI_SWIGLU_FWD) {
-                __nv_bfloat16* arow = p.d + grow * p.ldd + n0h;
-                __nv_bfloat16* prow = p.d2 ? p.d2 + grow * (2 * static_cast<int64_t>(p.inter)) + n0h : nullptr;
-                constexpr int kChunks = BN / 64 / 2;
-#pragma unroll 1
-                for (int c = half * kChunks; c < (half + 1) * kChunks; ++c) {
-                    const int cols_left = n_valid - c * 32;
-                    if (cols_left <= 0) break;
-                    float u[32], g[32];
-                    tc_load_32(taddr + c * 32, u);
-                    tc_load_32(taddr + BN / 2 + c * 32, g);
+                // This warp: 32 rows x 64 act columns of the half (up in accumulator columns [0,128), gate in
+                // [128,256)).  up and gate are rounded to bf16 and go through the patch one after the other;
+                // act = up * gate * sigmoid(gate) is computed from the rounded values in line form, and all three
+                // leave as whole 128-byte row segments (up and gate into `pre`, act into its own matrix).
+                const int col0 = half * 64;
+                const int cols_left = n_valid - col0;
+                if (cols_left > 0) {
+                    uint4 pg[8];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        u[i] = round_bf16(u[i]);
-                        g[i] = round_bf16(g[i]);
-                    }
-                    if (row_ok && prow) {
-                        store_row32_bf16(prow + c * 32, u, cols_left);
-                        store_row32_bf16(prow + p.inter + c * 32, g, cols_left);
-                    }
+                    for (int q = 0; q < 2; ++q) {
+                        float u[32], g[32];
+                        if (cols_left > q * 32) {
+                            tc_load_32(taddr + col0 + q * 32, u);
+                            tc_load_32(taddr + BN / 2 + col0 + q * 32, g);
+                        } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) u[i] = u[i] * g[i] * sigmoid_clamped_fast(g[i]);
-                    if (row_ok) store_row32_bf16(arow + c * 32, u, cols_left);
+                            for (int i = 0; i < 32; ++i) u[i] = g[i] = 0.f;
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            st_shared_16(patch_addr(patch, lane, q * 4 + k), pack8(u + k * 8, f16));
+                            pg[q * 4 + k] = pack8(g + k * 8, f16);
+                        }
+                    }
+                    __syncwarp();
+                    uint4 lu[8];
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) lu[it] = ld_shared_16(patch_addr(patch, it * 4 + lr, lp));
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) st_shared_16(patch_addr(patch, lane, j), pg[j]);
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + lr;
+                        const uint4 lg = ld_shared_16(patch_addr(patch, r, lp));
+                        const int row = quad * 32 + r;
+                        float u[8], g[8];
+                        unpack8(lu[it], u, f16);
+                        unpack8(lg, g, f16);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) u[i] = u[i] * g[i] * sigmoid_clamped_fast(g[i]);
+                        if (row < t.rows_valid && lp * 8 < cols_left) {
+                            const int64_t grow = t.d_row + row;
+                            const int col = n0h + col0 + lp * 8;
+                            if (p.d2 != nullptr) {
+                                st_global_16(p.d2 + grow * pre_pitch + col, lu[it]);
+                                st_global_16(p.d2 + grow * pre_pitch + p.inter + col, lg);
+                            }
+                            st_global_16(p.d + grow * p.ldd + col, pack8(u, f16));
+                        }
+                    }
+                    __syncwarp();
                 }
             } else {
-                const __nv_bfloat16* prow = p.pre + grow * (2 * static_cast<int64_t>(p.inter)) + n0h;
-                __nv_bfloat16* drow = p.d + grow * (2 * static_cast<int64_t>(p.inter)) + n0h;
-                constexpr int kChunks = BN / 32 / 2;
-                const int c_begin = half * kChunks, c_end = (half + 1) * kChunks;
-                uint4 nu[4], ng[4];
-                auto fetch = [&](int c) {
-                    const int cols_left = n_valid - c * 32;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const bool ok = row_ok && q * 8 < cols_left;
-                        nu[q] = ok ? ld_global_16(prow + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
-                        ng[q] = ok ? ld_global_16(prow + p.inter + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
-                    }
-                };
-                fetch(c_begin);
+                // d_act tile -> d_up, d_gate with the saved up / gate of the same rows and columns.  The math is
+                // elementwise, so it runs in line form: only d_act (rounded to bf16, as the unfused path would
+                // store it) goes through the patch; up and gate were loaded, and d_up and d_gate are stored, as
+                // whole 128-byte row segments.
 #pragma unroll 1
-                for (int c = c_begin; c < c_end; ++c) {
-                    const int cols_left = n_valid - c * 32;
+                for (int g = half * kGroups; g < (half + 1) * kGroups; ++g) {
+                    const int cols_left = n_valid - g * 64;
                     if (cols_left <= 0) break;
-                    float da[32], u[32], g[32];
-                    tc_load_32(taddr + c * 32, da);
+                    // the group after this one (same half, or the first of the next half)
+                    const bool same_half = g + 1 < (half + 1) * kGroups;
+                    const int nh = same_half ? h : h + 1, ng = same_half ? g + 1 : half * kGroups;
+                    const bool col_ok = lp * 8 < cols_left;
+                    const int col = n0h + g * 64 + lp * 8;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        Elem<__nv_bfloat16>::unpack(nu[q], u + q * 8);
-                        Elem<__nv_bfloat16>::unpack(ng[q], g + q * 8);
-                    }
-                    if (c + 1 < c_end) fetch(c + 1);
-                    if (row_ok) {
+                    for (int q = 0; q < 2; ++q) {
+                        float da[32];
+                        if (cols_left > q * 32) {
+                            tc_load_32(taddr + g * 64 + q * 32, da);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float d = round_bf16(da[i]);
-                            const float s = sigmoid_clamped_fast(g[i]);
-                            const float silu = g[i] * s;
-                            da[i] = d * silu;
-                            g[i] = d * u[i] * (s + silu * (1.f - s));
+                            for (int i = 0; i < 32; ++i) da[i] = 0.f;
                         }
-                        store_row32_bf16(drow + c * 32, da, cols_left);
-                        store_row32_bf16(drow + p.inter + c * 32, g, cols_left);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            st_shared_16(patch_addr(patch, lane, q * 4 + k), pack8(da + k * 8, f16));
                     }
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + lr;
+                        const int row = quad * 32 + r;
+                        float d[8], u[8], gt[8], du[8], dg[8];
+                        unpack8(ld_shared_16(patch_addr(patch, r, lp)), d, f16);
+                        unpack8(cu[it], u, f16);
+                        unpack8(cg[it], gt, f16);
+                        bwd_fetch(nh, ng, it);  // this step's registers are free: refill them for the next group
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float sg = sigmoid_clamped_fast(gt[i]);
+                            const float silu = gt[i] * sg;
+                            du[i] = d[i] * silu;
+                            dg[i] = d[i] * u[i] * (sg + silu * (1.f - sg));
+                        }
+                        if (col_ok && row < t.rows_valid) {
+                            __nv_bfloat16* dst = p.d + (t.d_row + row) * pre_pitch + col;
+                            st_global_16(dst, pack8(du, f16));
+                            st_global_16(dst + p.inter, pack8(dg, f16));
+                        }
+                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty_bar[hs]), 0));  // the leader's barrier
+            if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&acc_empty_bar[hs]), 0));  // the leader's barrier
             }  // halves
             if (!alive) break;
             acc_phase ^= 1u;
@@ -717,22 +775,9 @@ static int pair_skew() {
     return v;
 }
 
-// FMA_B200_GEMM_EPI_TMA=0 keeps the epilogues on per-row stores from registers (a measurement knob).
-static int tma_store_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* env = getenv("FMA_B200_GEMM_EPI_TMA");
-        v = (env != nullptr && atoi(env) == 0) ? 0 : 1;
-    }
-    return v;
-}
-
-// Output map of a rows-mode GEMM: [rows_cap, n_cols] with row pitch `pitch` elements.
+// Output map of a rows-mode GEMM with the plain epilogue: [rows_cap, n_cols] with row pitch `pitch` elements.
 static int encode_rows_output(GemmParams& p, const void* D, int64_t rows_cap, int n_cols, int64_t pitch) {
-    if (!tma_store_enabled()) return FMA_B200_OK;
-    if (int rc = encode_3d(&p.map_d, D, n_cols, rows_cap, 1, pitch, pitch, 64, 32)) return rc;
-    p.tma_store = 1;
-    return FMA_B200_OK;
+    return encode_3d(&p.map_d, D, n_cols, rows_cap, 1, pitch, pitch, 32, 32, p.f16 != 0);
 }
 
 template <bool A_MN, bool B_MN, int EPI, int HALVES = 2>
@@ -767,11 +812,12 @@ static int fill_pair_common(GemmParams& p) {
 }
 
 int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-                const int32_t* mtile_expert, bool narrow, cudaStream_t s) {
+                const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, PAIR_B_ROWS)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, PAIR_B_ROWS, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.d = static_cast<__nv_bfloat16*>(Y);
@@ -790,11 +836,12 @@ int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, 
 }
 
 int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                       const int32_t* mtile_expert, bool narrow, cudaStream_t s) {
+                       const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * 2 * I, IN, BK, PAIR_B_ROWS)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * 2 * I, IN, BK, PAIR_B_ROWS, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.d = static_cast<__nv_bfloat16*>(act);
@@ -814,11 +861,12 @@ int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64
 }
 
 int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* mtile_expert, bool swiglu, bool narrow, cudaStream_t s) {
+              const int32_t* mtile_expert, bool swiglu, bool narrow, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.d = static_cast<__nv_bfloat16*>(dX);
@@ -834,7 +882,8 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     p.n_groups = E;
     if (!swiglu) {
         if (int rc = encode_rows_output(p, dX, rows_cap, IN, IN)) return rc;
-    }
+    } else {
+        }
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
     if (narrow) {
         if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD, 1>(p, total, s);
@@ -848,11 +897,12 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
 // output width): the epilogue of the expert-parallel layer that returns rows straight into the arenas of the
 // ranks they came from.
 int tc2_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
-                     const int32_t* mtile_expert, cudaStream_t s) {
+                     const int32_t* mtile_expert, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, PAIR_B_ROWS)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, X, IN, rows_cap, IN, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, BK, PAIR_B_ROWS, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.mtile_dst = dst_table;
@@ -867,11 +917,12 @@ int tc2_forward_peer(const void* X, const void* W, const uint64_t* dst_table, in
 }
 
 int tc2_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
-                   const int32_t* mtile_expert, cudaStream_t s) {
+                   const int32_t* mtile_expert, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM)) return rc;
-    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, BK, BM, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, W, IN, static_cast<uint64_t>(E) * OUT, IN, 64, BK, f16)) return rc;
     p.mode = MODE_ROWS;
     p.mtile_expert = mtile_expert;
     p.mtile_dst = dst_table;
@@ -887,11 +938,12 @@ int tc2_dgrad_peer(const void* dY, const void* W, const uint64_t* dst_table, int
 }
 
 int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* seg_offsets, int n_seg, cudaStream_t s) {
+              const int32_t* seg_offsets, int n_seg, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
-    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, 64, BK)) return rc;
-    if (int rc = encode_2d(&p.map_b, X, IN, rows_cap, IN, 64, BK)) return rc;
+    p.f16 = f16 ? 1 : 0;
+    if (int rc = encode_2d(&p.map_a, dY, OUT, rows_cap, OUT, 64, BK, f16)) return rc;
+    if (int rc = encode_2d(&p.map_b, X, IN, rows_cap, IN, 64, BK, f16)) return rc;
     p.mode = MODE_WGRAD;
     p.seg_offsets = seg_offsets;
     p.n_seg = n_seg;
@@ -903,10 +955,8 @@ int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, 
     p.n_ntiles = (IN + 2 * BN - 1) / (2 * BN);
     p.n_cols = IN;
     p.n_groups = E;
-    if (tma_store_enabled()) {  // dW as {IN, OUT, E}: rows of a tile beyond OUT are clipped, not written into the next expert
-        if (int rc = encode_3d(&p.map_d, dW, IN, OUT, E, IN, static_cast<uint64_t>(OUT) * IN, 64, 32)) return rc;
-        p.tma_store = 1;
-    }
+    // dW as {IN, OUT, E}: rows of a tile beyond OUT are clipped, not written into the next expert
+    if (int rc = encode_3d(&p.map_d, dW, IN, OUT, E, IN, static_cast<uint64_t>(OUT) * IN, 32, 32, f16)) return rc;
     const int64_t total = static_cast<int64_t>(E) * ((p.mtiles_per_group + 1) / 2) * p.n_ntiles;
     return launch_pair<true, true, EPI_PLAIN>(p, total, s);
 }

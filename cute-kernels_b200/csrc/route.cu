@@ -79,17 +79,9 @@ static RouteWorkspace carve_workspace(void* workspace, int E) {
 // top-k + softmax
 // ---------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ float load_as_float(const T* p);
-template <>
-__device__ __forceinline__ float load_as_float<float>(const float* p) { return *p; }
-template <>
-__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float load_as_float(const T* p) { return elem_to_float<T>(*p); }
 template <typename T>
-__device__ __forceinline__ void store_from_float(T* p, float v);
-template <>
-__device__ __forceinline__ void store_from_float<float>(float* p, float v) { *p = v; }
-template <>
-__device__ __forceinline__ void store_from_float<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void store_from_float(T* p, float v) { *p = float_to_elem<T>(v); }
 
 // Order-preserving map of a float to an unsigned key: a > b  <=>  key(a) > key(b).  NaN maps to the
 // largest key, as torch.topk orders it; -0 and +0 share a key; every key of a real input is > 0.
@@ -129,15 +121,30 @@ topk_softmax_kernel(const T* __restrict__ logits, int64_t rows, int E, int k, in
 
     const int64_t row0 = piece * tokens_per_piece;
     const int64_t row1 = (row0 + tokens_per_piece < rows) ? row0 + tokens_per_piece : rows;
+    // The logits of the next token are in flight while the current one is processed (a warp walks its
+    // tokens one after the other, so an unhidden load would cost a memory round trip per token).
+    float nv[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+        const int c = lane + 32 * i;
+        nv[i] = (c < E && row0 < row1) ? load_as_float(logits + row0 * E + c) : 0.f;
+    }
     for (int64_t row = row0; row < row1; ++row) {
-        const T* src = logits + row * E;
         float v[kPerLane];
         uint32_t key[kPerLane];
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
             const int c = lane + 32 * i;
-            v[i] = (c < E) ? load_as_float(src + c) : 0.f;
+            v[i] = nv[i];
             key[i] = (c < E) ? order_key(v[i]) : 0u;  // 0 = never selected
+        }
+        if (row + 1 < row1) {
+            const T* nsrc = logits + (row + 1) * E;
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) {
+                const int c = lane + 32 * i;
+                if (c < E) nv[i] = load_as_float(nsrc + c);
+            }
         }
         uint32_t my_key = 0;  // lane r keeps the r-th selection
         int my_idx = 0;
@@ -603,10 +610,12 @@ int fma_b200_router_topk_softmax(const void* logits, int32_t dtype, int64_t T, i
     FMAB_REQUIRE(logits && weights && selected, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const RoutePlan plan = make_plan(T * k, E, k);
-    if (dtype == FMA_B200_F32) return launch_topk<float>(logits, T, E, k, weights, selected, plan, nullptr, nullptr, s);
-    if (dtype == FMA_B200_BF16)
-        return launch_topk<__nv_bfloat16>(logits, T, E, k, weights, selected, plan, nullptr, nullptr, s);
-    return fail(FMA_B200_ERR_UNSUPPORTED, "router_topk_softmax: dtype %d", dtype);
+    int rc = FMA_B200_OK;
+    if (!dispatch_dtype(dtype, [&](auto tag) {
+            rc = launch_topk<decltype(tag)>(logits, T, E, k, weights, selected, plan, nullptr, nullptr, s);
+        }))
+        return fail(FMA_B200_ERR_UNSUPPORTED, "router_topk_softmax: dtype %d", dtype);
+    return rc;
 }
 
 int fma_b200_router_topk_softmax_routed(const void* logits, int32_t dtype, int64_t T, int32_t E, int32_t k,
@@ -624,10 +633,12 @@ int fma_b200_router_topk_softmax_routed(const void* logits, int32_t dtype, int64
     const RoutePlan plan = make_plan(T * k, E, k);
     const RouteWorkspace ws = carve_workspace(sort_workspace, E);
     float* prob = want_probs ? ws.prob : nullptr;
-    if (dtype == FMA_B200_F32) return launch_topk<float>(logits, T, E, k, weights, selected, plan, ws.hist, prob, s);
-    if (dtype == FMA_B200_BF16)
-        return launch_topk<__nv_bfloat16>(logits, T, E, k, weights, selected, plan, ws.hist, prob, s);
-    return fail(FMA_B200_ERR_UNSUPPORTED, "router_topk_softmax_routed: dtype %d", dtype);
+    int rc = FMA_B200_OK;
+    if (!dispatch_dtype(dtype, [&](auto tag) {
+            rc = launch_topk<decltype(tag)>(logits, T, E, k, weights, selected, plan, ws.hist, prob, s);
+        }))
+        return fail(FMA_B200_ERR_UNSUPPORTED, "router_topk_softmax_routed: dtype %d", dtype);
+    return rc;
 }
 
 int fma_b200_router_topk_softmax_backward(const void* weights, const void* d_weights, const int64_t* selected,
@@ -640,15 +651,12 @@ int fma_b200_router_topk_softmax_backward(const void* weights, const void* d_wei
     FMAB_REQUIRE(weights && d_weights && selected && d_logits, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned grid = static_cast<unsigned>((T + kRouteWarps - 1) / kRouteWarps);
-    if (dtype == FMA_B200_F32)
-        topk_softmax_backward_kernel<float><<<grid, kRouteThreads, 0, s>>>(
-            static_cast<const float*>(weights), static_cast<const float*>(d_weights), selected, T, E, k,
-            static_cast<float*>(d_logits));
-    else if (dtype == FMA_B200_BF16)
-        topk_softmax_backward_kernel<__nv_bfloat16><<<grid, kRouteThreads, 0, s>>>(
-            static_cast<const __nv_bfloat16*>(weights), static_cast<const __nv_bfloat16*>(d_weights), selected, T, E,
-            k, static_cast<__nv_bfloat16*>(d_logits));
-    else
+    if (!dispatch_dtype(dtype, [&](auto tag) {
+            using Elt = decltype(tag);
+            topk_softmax_backward_kernel<Elt><<<grid, kRouteThreads, 0, s>>>(
+                static_cast<const Elt*>(weights), static_cast<const Elt*>(d_weights), selected, T, E, k,
+                static_cast<Elt*>(d_logits));
+        }))
         return fail(FMA_B200_ERR_UNSUPPORTED, "router_topk_softmax_backward: dtype %d", dtype);
     return check_launch("router_topk_softmax_backward");
 }
@@ -661,9 +669,12 @@ int fma_b200_router_mean_prob_backward(const void* logits, const float* d_mean_p
     if (T == 0) return FMA_B200_OK;
     FMAB_REQUIRE(logits && d_mean_prob && d_logits, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_F32) return launch_prob_backward<float>(logits, d_mean_prob, T, E, d_logits, s);
-    if (dtype == FMA_B200_BF16) return launch_prob_backward<__nv_bfloat16>(logits, d_mean_prob, T, E, d_logits, s);
-    return fail(FMA_B200_ERR_UNSUPPORTED, "router_mean_prob_backward: dtype %d", dtype);
+    int rc = FMA_B200_OK;
+    if (!dispatch_dtype(dtype, [&](auto tag) {
+            rc = launch_prob_backward<decltype(tag)>(logits, d_mean_prob, T, E, d_logits, s);
+        }))
+        return fail(FMA_B200_ERR_UNSUPPORTED, "router_mean_prob_backward: dtype %d", dtype);
+    return rc;
 }
 
 int64_t fma_b200_moe_rows_cap(int64_t R, int32_t E, int32_t row_align) {

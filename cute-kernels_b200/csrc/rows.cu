@@ -79,8 +79,7 @@ gather_sum_kernel(const T* __restrict__ grouped, const T* __restrict__ coeff, in
     if (lane < k) {
         my_row = row_of_slot[t * k + lane];
         if (coeff != nullptr) {
-            const T c = coeff[t * k + lane];
-            if constexpr (sizeof(T) == 2) my_w = __bfloat162float(c); else my_w = c;
+            my_w = elem_to_float<T>(coeff[t * k + lane]);
         }
     }
     uint4* dst = reinterpret_cast<uint4*>(out + t * H);
@@ -135,15 +134,10 @@ combine_backward_kernel(const T* __restrict__ dy, const T* __restrict__ expert_o
     for (int j = 0; j < k; ++j) {
         const int64_t row = row_of_slot[t * k + j];
         if (row < 0) {  // slot without a row: no gradient row to write, zero gradient for its weight
-            if (want_dw && lane == 0) {
-                if constexpr (sizeof(T) == 2) d_weights[t * k + j] = __float2bfloat16_rn(0.f);
-                else d_weights[t * k + j] = 0.f;
-            }
+            if (want_dw && lane == 0) d_weights[t * k + j] = float_to_elem<T>(0.f);
             continue;
         }
-        const T wt = weights[t * k + j];
-        float w;
-        if constexpr (sizeof(T) == 2) w = __bfloat162float(wt); else w = wt;
+        const float w = elem_to_float<T>(weights[t * k + j]);
         uint4* dst = reinterpret_cast<uint4*>(d_expert_out + row * H);
         const uint4* o_src = want_dw ? reinterpret_cast<const uint4*>(expert_out + row * H) : nullptr;
         float dot = 0.f;
@@ -177,10 +171,7 @@ combine_backward_kernel(const T* __restrict__ dy, const T* __restrict__ expert_o
         }
         if (want_dw) {
             dot = warp_sum(dot);
-            if (lane == 0) {
-                if constexpr (sizeof(T) == 2) d_weights[t * k + j] = __float2bfloat16_rn(dot);
-                else d_weights[t * k + j] = dot;
-            }
+            if (lane == 0) d_weights[t * k + j] = float_to_elem<T>(dot);
         }
     }
 }
@@ -224,8 +215,7 @@ bias_grad_kernel(const T* __restrict__ d_grouped, int C, const int32_t* __restri
         float v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const T x = d_grouped[(r + u) * C + c];
-            if constexpr (sizeof(T) == 2) v[u] = __bfloat162float(x); else v[u] = x;
+            v[u] = elem_to_float<T>(d_grouped[(r + u) * C + c]);
         }
         acc += v[0];
         acc += v[1];
@@ -233,18 +223,16 @@ bias_grad_kernel(const T* __restrict__ d_grouped, int C, const int32_t* __restri
         acc += v[3];
     }
     for (; r < end; ++r) {
-        const T x = d_grouped[r * C + c];
-        if constexpr (sizeof(T) == 2) acc += __bfloat162float(x); else acc += x;
+        acc += elem_to_float<T>(d_grouped[r * C + c]);
     }
-    if constexpr (sizeof(T) == 2) d_bias[static_cast<int64_t>(e) * C + c] = __float2bfloat16_rn(acc);
-    else d_bias[static_cast<int64_t>(e) * C + c] = acc;
+    d_bias[static_cast<int64_t>(e) * C + c] = float_to_elem<T>(acc);
 }
 
 static int check_rows_args(int32_t dtype, int64_t T, int32_t H, int32_t k) {
-    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    FMAB_REQUIRE(known_dtype(dtype), FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
     FMAB_REQUIRE(T >= 0 && T < (1LL << 31), FMA_B200_ERR_BAD_ARG, "T=%lld", (long long)T);
     FMAB_REQUIRE(k >= 1 && k <= kMaxTopK, FMA_B200_ERR_BAD_ARG, "k=%d not in [1,%d]", k, kMaxTopK);
-    const int per_vec = (dtype == FMA_B200_F32) ? 4 : 8;
+    const int per_vec = elems_per_16_bytes(dtype);
     FMAB_REQUIRE(H >= per_vec && H % per_vec == 0, FMA_B200_ERR_BAD_ARG, "H=%d is not a multiple of 16 bytes", H);
     return FMA_B200_OK;
 }
@@ -268,14 +256,11 @@ int fma_b200_moe_scatter(const void* x, int32_t dtype, int64_t T, int32_t H, int
     const int64_t grid = tok_blocks + pad_blocks;
     if (grid == 0) return FMA_B200_OK;
     FMAB_REQUIRE(grid < (1LL << 31), FMA_B200_ERR_BAD_ARG, "grid too large");
-    if (dtype == FMA_B200_F32)
-        scatter_kernel<float><<<(unsigned)grid, kRowThreads, 0, s>>>(static_cast<const float*>(x), T, H, k, row_of_slot,
-                                                                    slot_of_row, pad_offsets, E, tok_blocks,
-                                                                    static_cast<float*>(grouped));
-    else
-        scatter_kernel<__nv_bfloat16><<<(unsigned)grid, kRowThreads, 0, s>>>(
-            static_cast<const __nv_bfloat16*>(x), T, H, k, row_of_slot, slot_of_row, pad_offsets, E, tok_blocks,
-            static_cast<__nv_bfloat16*>(grouped));
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        scatter_kernel<Elt><<<(unsigned)grid, kRowThreads, 0, s>>>(static_cast<const Elt*>(x), T, H, k, row_of_slot, slot_of_row,
+                                                                  pad_offsets, E, tok_blocks, static_cast<Elt*>(grouped));
+    });
     return check_launch("moe_scatter");
 }
 
@@ -288,14 +273,11 @@ static int launch_gather_sum(const void* grouped, const void* coeff, int32_t dty
     FMAB_REQUIRE(aligned16(grouped) && aligned16(out), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned grid = static_cast<unsigned>((T + kRowWarps - 1) / kRowWarps);
-    if (dtype == FMA_B200_F32)
-        gather_sum_kernel<float><<<grid, kRowThreads, 0, s>>>(static_cast<const float*>(grouped),
-                                                             static_cast<const float*>(coeff), T, H, k, row_of_slot,
-                                                             static_cast<float*>(out));
-    else
-        gather_sum_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(
-            static_cast<const __nv_bfloat16*>(grouped), static_cast<const __nv_bfloat16*>(coeff), T, H, k,
-            row_of_slot, static_cast<__nv_bfloat16*>(out));
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        gather_sum_kernel<Elt><<<grid, kRowThreads, 0, s>>>(static_cast<const Elt*>(grouped), static_cast<const Elt*>(coeff), T,
+                                                           H, k, row_of_slot, static_cast<Elt*>(out));
+    });
     return check_launch(what);
 }
 
@@ -328,24 +310,21 @@ int fma_b200_moe_combine_backward(const void* dy, const void* expert_out, const 
     const int64_t grid = tok_blocks + pad_blocks;
     if (grid == 0) return FMA_B200_OK;
     FMAB_REQUIRE(grid < (1LL << 31), FMA_B200_ERR_BAD_ARG, "grid too large");
-    if (dtype == FMA_B200_F32)
-        combine_backward_kernel<float><<<(unsigned)grid, kRowThreads, 0, s>>>(
-            static_cast<const float*>(dy), static_cast<const float*>(expert_out), static_cast<const float*>(weights), T,
-            H, k, row_of_slot, slot_of_row, pad_offsets, E, tok_blocks, static_cast<float*>(d_expert_out),
-            static_cast<float*>(d_weights));
-    else
-        combine_backward_kernel<__nv_bfloat16><<<(unsigned)grid, kRowThreads, 0, s>>>(
-            static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(expert_out),
-            static_cast<const __nv_bfloat16*>(weights), T, H, k, row_of_slot, slot_of_row, pad_offsets, E, tok_blocks,
-            static_cast<__nv_bfloat16*>(d_expert_out), static_cast<__nv_bfloat16*>(d_weights));
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        combine_backward_kernel<Elt><<<(unsigned)grid, kRowThreads, 0, s>>>(
+            static_cast<const Elt*>(dy), static_cast<const Elt*>(expert_out), static_cast<const Elt*>(weights), T, H, k,
+            row_of_slot, slot_of_row, pad_offsets, E, tok_blocks, static_cast<Elt*>(d_expert_out),
+            static_cast<Elt*>(d_weights));
+    });
     return check_launch("moe_combine_backward");
 }
 
 int fma_b200_moe_bias_add(void* grouped, const void* bias, int32_t dtype, int64_t rows_cap, int32_t C,
                           const int32_t* mtile_expert, const int32_t* slot_of_row, void* stream) {
     using namespace fmab;
-    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
-    const int per_vec = (dtype == FMA_B200_F32) ? 4 : 8;
+    FMAB_REQUIRE(known_dtype(dtype), FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    const int per_vec = elems_per_16_bytes(dtype);
     FMAB_REQUIRE(C >= per_vec && C % per_vec == 0, FMA_B200_ERR_BAD_ARG, "C=%d is not a multiple of 16 bytes", C);
     FMAB_REQUIRE(rows_cap >= 0 && rows_cap % 128 == 0, FMA_B200_ERR_BAD_ARG, "rows_cap=%lld", (long long)rows_cap);
     if (rows_cap == 0) return FMA_B200_OK;
@@ -353,30 +332,26 @@ int fma_b200_moe_bias_add(void* grouped, const void* bias, int32_t dtype, int64_
     FMAB_REQUIRE(aligned16(grouped) && aligned16(bias), FMA_B200_ERR_BAD_ARG, "pointers not 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned grid = static_cast<unsigned>((rows_cap + kRowWarps - 1) / kRowWarps);
-    if (dtype == FMA_B200_F32)
-        bias_add_kernel<float><<<grid, kRowThreads, 0, s>>>(static_cast<float*>(grouped), static_cast<const float*>(bias),
-                                                           rows_cap, C, mtile_expert, slot_of_row);
-    else
-        bias_add_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(static_cast<__nv_bfloat16*>(grouped),
-                                                                   static_cast<const __nv_bfloat16*>(bias), rows_cap, C,
-                                                                   mtile_expert, slot_of_row);
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        bias_add_kernel<Elt><<<grid, kRowThreads, 0, s>>>(static_cast<Elt*>(grouped), static_cast<const Elt*>(bias), rows_cap,
+                                                         C, mtile_expert, slot_of_row);
+    });
     return check_launch("moe_bias_add");
 }
 
 int fma_b200_moe_bias_grad(const void* d_grouped, int32_t dtype, int32_t E, int32_t C, const int32_t* pad_offsets,
                            void* d_bias, void* stream) {
     using namespace fmab;
-    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    FMAB_REQUIRE(known_dtype(dtype), FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
     FMAB_REQUIRE(E >= 1 && E <= 65535 && C >= 1, FMA_B200_ERR_BAD_ARG, "E=%d C=%d", E, C);
     FMAB_REQUIRE(d_grouped && pad_offsets && d_bias, FMA_B200_ERR_BAD_ARG, "NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid((C + 255) / 256, E);
-    if (dtype == FMA_B200_F32)
-        bias_grad_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(d_grouped), C, pad_offsets,
-                                                    static_cast<float*>(d_bias));
-    else
-        bias_grad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(d_grouped), C,
-                                                            pad_offsets, static_cast<__nv_bfloat16*>(d_bias));
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        bias_grad_kernel<Elt><<<grid, 256, 0, s>>>(static_cast<const Elt*>(d_grouped), C, pad_offsets, static_cast<Elt*>(d_bias));
+    });
     return check_launch("moe_bias_grad");
 }
 

@@ -58,9 +58,9 @@ static int swiglu_grid(int64_t total_vec) {
 
 static int check_swiglu(int32_t dtype, int64_t rows, int64_t cols, const int64_t* pitches, int n_pitch,
                         const void* const* ptrs, int n_ptr) {
-    FMAB_REQUIRE(dtype == FMA_B200_F32 || dtype == FMA_B200_BF16, FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
+    FMAB_REQUIRE(known_dtype(dtype), FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
     FMAB_REQUIRE(rows >= 0 && cols >= 0, FMA_B200_ERR_BAD_ARG, "rows=%lld cols=%lld", (long long)rows, (long long)cols);
-    const int per_vec = (dtype == FMA_B200_F32) ? 4 : 8;
+    const int per_vec = elems_per_16_bytes(dtype);
     FMAB_REQUIRE(cols % per_vec == 0, FMA_B200_ERR_BAD_ARG, "cols=%lld is not a multiple of 16 bytes", (long long)cols);
     for (int i = 0; i < n_pitch; ++i)
         FMAB_REQUIRE(pitches[i] >= cols && pitches[i] % per_vec == 0, FMA_B200_ERR_BAD_ARG, "pitch %d = %lld invalid", i,
@@ -83,17 +83,13 @@ int fma_b200_swiglu_forward(const void* gate, int64_t gate_pitch, const void* up
     if (int rc = check_swiglu(dtype, rows, cols, pitches, 3, ptrs, 3)) return rc;
     if (rows * cols == 0) return FMA_B200_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_F32) {
-        const int64_t vpr = cols / 4;
-        swiglu_forward_kernel<float><<<swiglu_grid(rows * vpr), kSwigluThreads, 0, s>>>(
-            static_cast<const float*>(gate), gate_pitch, static_cast<const float*>(up), up_pitch,
-            static_cast<float*>(out), out_pitch, rows, vpr);
-    } else {
-        const int64_t vpr = cols / 8;
-        swiglu_forward_kernel<__nv_bfloat16><<<swiglu_grid(rows * vpr), kSwigluThreads, 0, s>>>(
-            static_cast<const __nv_bfloat16*>(gate), gate_pitch, static_cast<const __nv_bfloat16*>(up), up_pitch,
-            static_cast<__nv_bfloat16*>(out), out_pitch, rows, vpr);
-    }
+    const int64_t vpr = cols / elems_per_16_bytes(dtype);
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        swiglu_forward_kernel<Elt><<<swiglu_grid(rows * vpr), kSwigluThreads, 0, s>>>(
+            static_cast<const Elt*>(gate), gate_pitch, static_cast<const Elt*>(up), up_pitch, static_cast<Elt*>(out),
+            out_pitch, rows, vpr);
+    });
     return check_launch("swiglu_forward");
 }
 
@@ -106,19 +102,13 @@ int fma_b200_swiglu_backward(const void* gate, int64_t gate_pitch, const void* u
     if (int rc = check_swiglu(dtype, rows, cols, pitches, 5, ptrs, 5)) return rc;
     if (rows * cols == 0) return FMA_B200_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == FMA_B200_F32) {
-        const int64_t vpr = cols / 4;
-        swiglu_backward_kernel<float><<<swiglu_grid(rows * vpr), kSwigluThreads, 0, s>>>(
-            static_cast<const float*>(gate), gate_pitch, static_cast<const float*>(up), up_pitch,
-            static_cast<const float*>(dy), dy_pitch, static_cast<float*>(gate_grad), gate_grad_pitch,
-            static_cast<float*>(up_grad), up_grad_pitch, rows, vpr);
-    } else {
-        const int64_t vpr = cols / 8;
-        swiglu_backward_kernel<__nv_bfloat16><<<swiglu_grid(rows * vpr), kSwigluThreads, 0, s>>>(
-            static_cast<const __nv_bfloat16*>(gate), gate_pitch, static_cast<const __nv_bfloat16*>(up), up_pitch,
-            static_cast<const __nv_bfloat16*>(dy), dy_pitch, static_cast<__nv_bfloat16*>(gate_grad), gate_grad_pitch,
-            static_cast<__nv_bfloat16*>(up_grad), up_grad_pitch, rows, vpr);
-    }
+    const int64_t vpr = cols / elems_per_16_bytes(dtype);
+    dispatch_dtype(dtype, [&](auto tag) {
+        using Elt = decltype(tag);
+        swiglu_backward_kernel<Elt><<<swiglu_grid(rows * vpr), kSwigluThreads, 0, s>>>(
+            static_cast<const Elt*>(gate), gate_pitch, static_cast<const Elt*>(up), up_pitch, static_cast<const Elt*>(dy),
+            dy_pitch, static_cast<Elt*>(gate_grad), gate_grad_pitch, static_cast<Elt*>(up_grad), up_grad_pitch, rows, vpr);
+    });
     return check_launch("swiglu_backward");
 }
 

@@ -338,6 +338,7 @@ class ExpertParallelMoE(MoE):
         self.fuse_return = fuse_return
         self.last_transport = None  # "peer" or "nccl": what the most recent forward used
         self._arena = None
+        self._sm_reserved = False
         self._peer_unavailable = None  # reason text once the peer transport has been given up
         self.ep_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.ep_rank = dist.get_rank(process_group) if dist.is_initialized() else 0
@@ -417,6 +418,12 @@ class ExpertParallelMoE(MoE):
         plan = P.PeerPlan(counts, self.ep_rank, self.overlap_chunks)
         if max(plan.total_recv_rows) > arena.recv_cap:  # the same plan on every rank
             return None
+        if not self._sm_reserved:
+            # The flag kernels of the side stream must find a free SM while a persistent grouped GEMM runs,
+            # and a GEMM CTA fills its SM's shared memory: leave one CTA pair's worth of SMs out of the GEMM grids.
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            K.call("fma_b200_set_sm_limit", sms - 2)
+            self._sm_reserved = True
         return P._EPPeerSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
                                             arena, plan, gathered[:, :E].contiguous(), self.fuse_return)  # fmt: skip
 

@@ -43,8 +43,14 @@ FLAG_BYTES = 4 * 4 * MAX_CHUNKS * MAX_RANKS
 WAIT_TIMEOUT_MS = int(os.environ.get("FMA_B200_PEER_TIMEOUT_MS", "2000"))
 
 
-# Where the arena comes from: "ipc" = cudaMalloc + CUDA IPC through this library, "symm" = torch symmetric memory.
-ARENA_ALLOCATOR = os.environ.get("FMA_B200_PEER_ALLOC", "ipc")
+# Where the arena comes from: "ipc" = cudaMalloc + CUDA IPC through this library (every process then holds a
+# context on every GPU whose arena it maps), "symm" = torch symmetric memory (driver virtual-memory API: peer
+# memory is mapped into the process's own context).  Default: ipc for 2 ranks, symm above.
+ARENA_ALLOCATOR = os.environ.get("FMA_B200_PEER_ALLOC", "auto")
+# This transport uses plain peer loads and stores only.  Keep torch from binding the arena to an NVLink
+# multicast object as well (it is never used here, and memory bound to one makes an abnormal exit of one
+# rank a fault on the others); _allocate_symm refuses an arena that still came with one.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 _DEBUG = os.environ.get("FMA_B200_PEER_DEBUG", "0") == "1"
 
 
@@ -172,7 +178,9 @@ class PeerArena:
 
         self.local_ptr, self.peer_ptrs = 0, []
         self._symm = None  # (tensor, handle) when the arena comes from torch's symmetric memory
-        if ARENA_ALLOCATOR == "symm":
+        allocator = ARENA_ALLOCATOR if ARENA_ALLOCATOR in ("ipc", "symm") else ("ipc" if self.world_size <= 2 else "symm")
+        self.allocator = allocator
+        if allocator == "symm":
             self._allocate_symm()
         else:
             self._allocate_ipc()
@@ -246,6 +254,11 @@ class PeerArena:
                 tensor.zero_()
         except Exception as e:  # every rank fails or none: rendezvous is collective
             raise PeerTransportUnavailable(f"symmetric memory: {e}") from e
+        if int(getattr(handle, "multicast_ptr", 0) or 0) != 0:
+            # every rank sees the same: the binding is collective
+            del handle, tensor
+            raise PeerTransportUnavailable("symmetric memory came bound to an NVLink multicast object "
+                                           "(TORCH_SYMM_MEM_DISABLE_MULTICAST had no effect)")
         self._symm = (tensor, handle)
         self.local_ptr = tensor.data_ptr()
         self.peer_ptrs = [int(p) for p in handle.buffer_ptrs]

@@ -32,6 +32,7 @@ extern "C" {
 /* ---- element types ------------------------------------------------------- */
 #define FMA_B200_F32 0
 #define FMA_B200_BF16 1
+#define FMA_B200_F16 2 /* IEEE half: the reference's ops are dtype-generic (fma/include/dtypes/fp16.h) */
 
 /* Text for a status code; never NULL. */
 const char* fma_b200_status_string(int status);
