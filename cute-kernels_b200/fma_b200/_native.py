@@ -18,6 +18,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libfma_b200.so"
 
 F32 = 0
 BF16 = 1
+F16 = 2
 
 _I32, _I64, _P = c_int32, c_int64, c_void_p
 
@@ -68,6 +69,8 @@ SIGNATURES: dict[str, tuple] = {
         ctypes.c_int,
         [_P, _I64, _P, _I64, _P, _I64, _P, _I64, _P, _I64, _I32, _I64, _I64, _P],
     ),
+    "fma_b200_pack_sequence": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I32, _P]),
+    "fma_b200_unpack_sequence": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I32, _P]),
     "fma_b200_moe_gemm_forward": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
     "fma_b200_moe_gemm_dgrad": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
     "fma_b200_moe_gemm_wgrad": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
@@ -164,7 +167,9 @@ def dtype_code(dtype: torch.dtype) -> int:
         return F32
     if dtype == torch.bfloat16:
         return BF16
-    raise RuntimeError(f"unsupported dtype {dtype}: the B200 kernels handle float32 and bfloat16")
+    if dtype == torch.float16:
+        return F16
+    raise RuntimeError(f"unsupported dtype {dtype}: the B200 kernels handle float32, bfloat16 and float16")
 
 
 def require_cuda(*tensors: torch.Tensor) -> None:

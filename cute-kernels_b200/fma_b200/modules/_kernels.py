@@ -215,12 +215,12 @@ def gemm_wgrad(dY: torch.Tensor, X: torch.Tensor, E: int, seg_offsets: torch.Ten
 
 def gemm_forward_swiglu(X: torch.Tensor, W: torch.Tensor, mtile_expert: torch.Tensor, keep_pre: bool = True,
                         row_align: int = ROW_ALIGN):
-    """Up projection + SwiGLU.  bf16: one fused tcgen05 kernel; f32: GEMM then the swiglu kernel."""
+    """Up projection + SwiGLU.  bf16 / fp16: one fused tcgen05 kernel; f32: GEMM then the swiglu kernel."""
     E, twoI, IN = W.shape
     I = twoI // 2
     rows = X.size(0)
     dev = X.device
-    if X.dtype == torch.bfloat16:
+    if X.dtype in (torch.bfloat16, torch.float16):
         pre = torch.empty(rows, twoI, dtype=X.dtype, device=dev) if keep_pre else None
         act = torch.empty(rows, I, dtype=X.dtype, device=dev)
         call("fma_b200_moe_gemm_forward_swiglu", ptr(X), ptr(W), ptr(pre), ptr(act), dtype_code(X.dtype), rows, E, I,
@@ -241,7 +241,7 @@ def gemm_dgrad_swiglu(d_out: torch.Tensor, W: torch.Tensor, pre: torch.Tensor, m
     rows = d_out.size(0)
     dev = d_out.device
     d_pre = torch.empty(rows, 2 * I, dtype=d_out.dtype, device=dev)
-    if d_out.dtype == torch.bfloat16:
+    if d_out.dtype in (torch.bfloat16, torch.float16):
         call("fma_b200_moe_gemm_dgrad_swiglu", ptr(d_out), ptr(W), ptr(pre), ptr(d_pre), dtype_code(d_out.dtype), rows,
              E, OUT, I, ptr(mtile_expert), row_align, stream_ptr(dev))  # fmt: skip
         return d_pre

@@ -143,3 +143,170 @@ def _experts_backward(ctx, dy, *_unused):
 
 torch.library.register_autograd(f"{LIBRARY_NAME}::moe_swiglu_experts", _experts_backward,
                                 setup_context=_experts_setup)  # fmt: skip
+
+
+# ---- general experts (any activation, optional bias): sort, scatter, expert linear, combine as separate ops ----
+# Used by the traced layer when the activation is not swiglu_packed or the experts have a bias: the activation
+# itself stays ordinary traced PyTorch code between two expert-linear ops.
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_sort_maps", mutates_args=())
+def moe_sort_maps(selected: torch.Tensor, route_workspace: torch.Tensor, num_experts: int,
+                  row_align: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (expert_count, pad_offsets, row_of_slot, slot_of_row, mtile_expert)."""
+    with torch.cuda.device(selected.device):
+        m = K.moe_sort(selected, num_experts, row_align=row_align, routed_workspace=route_workspace)
+    return m.expert_count, m.pad_offsets, m.row_of_slot, m.slot_of_row, m.mtile_expert
+
+
+@moe_sort_maps.register_fake
+def _(selected, route_workspace, num_experts, row_align):
+    R = selected.numel()
+    cap = K.rows_cap(R, num_experts, row_align)
+    i32 = lambda *shape: selected.new_empty(shape, dtype=torch.int32)  # noqa: E731
+    return (selected.new_empty((num_experts,), dtype=torch.uint32), i32(num_experts + 1), i32(R), i32(cap),
+            i32(cap // 128))  # fmt: skip
+
+
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_scatter_rows", mutates_args=())
+def moe_scatter_rows(x: torch.Tensor, pad_offsets: torch.Tensor, row_of_slot: torch.Tensor, slot_of_row: torch.Tensor,
+                     mtile_expert: torch.Tensor, top_k: int, row_align: int) -> torch.Tensor:
+    with torch.cuda.device(x.device):
+        return K.scatter(x.contiguous(), _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align))
+
+
+@moe_scatter_rows.register_fake
+def _(x, pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align):
+    return x.new_empty(slot_of_row.size(0), x.size(1))
+
+
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_scatter_rows_backward", mutates_args=())
+def moe_scatter_rows_backward(d_grouped: torch.Tensor, pad_offsets: torch.Tensor, row_of_slot: torch.Tensor,
+                              slot_of_row: torch.Tensor, mtile_expert: torch.Tensor, top_k: int, row_align: int,
+                              num_tokens: int) -> torch.Tensor:
+    with torch.cuda.device(d_grouped.device):
+        maps = _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align)
+        return K.scatter_backward(d_grouped.contiguous(), maps, num_tokens)
+
+
+@moe_scatter_rows_backward.register_fake
+def _(d_grouped, pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align, num_tokens):
+    return d_grouped.new_empty(num_tokens, d_grouped.size(1))
+
+
+def _scatter_setup(ctx, inputs, output):
+    x, pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align = inputs
+    ctx.save_for_backward(pad_offsets, row_of_slot, slot_of_row, mtile_expert)
+    ctx.top_k, ctx.row_align, ctx.num_tokens = top_k, row_align, x.size(0)
+
+
+def _scatter_backward(ctx, d_grouped):
+    d_x = moe_scatter_rows_backward(d_grouped, *ctx.saved_tensors, ctx.top_k, ctx.row_align, ctx.num_tokens)
+    return d_x, None, None, None, None, None, None
+
+
+torch.library.register_autograd(f"{LIBRARY_NAME}::moe_scatter_rows", _scatter_backward, setup_context=_scatter_setup)
+
+
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_expert_linear", mutates_args=())
+def moe_expert_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, pad_offsets: torch.Tensor,
+                      row_of_slot: torch.Tensor, slot_of_row: torch.Tensor, mtile_expert: torch.Tensor, top_k: int,
+                      row_align: int) -> torch.Tensor:
+    """y[p] = x[p] . weight[e(p)]^T (+ bias[e(p)] on token rows) over the grouped layout."""
+    with torch.cuda.device(x.device):
+        y = K.gemm_forward(x.contiguous(), weight.contiguous(), mtile_expert, row_align)
+        if bias is not None:
+            K.bias_add_(y, bias.contiguous(), _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align))
+    return y
+
+
+@moe_expert_linear.register_fake
+def _(x, weight, bias, pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align):
+    return x.new_empty(x.size(0), weight.size(1))
+
+
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_expert_linear_backward", mutates_args=())
+def moe_expert_linear_backward(d_y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, pad_offsets: torch.Tensor,
+                               row_of_slot: torch.Tensor, slot_of_row: torch.Tensor, mtile_expert: torch.Tensor,
+                               top_k: int, row_align: int, need_x: bool, need_w: bool,
+                               need_b: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (d_x, d_weight, d_bias); a gradient that is not needed comes back empty."""
+    none = lambda: d_y.new_empty(0)  # noqa: E731
+    with torch.cuda.device(d_y.device):
+        d_y = d_y.contiguous()
+        maps = _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align)
+        d_x = K.gemm_dgrad(d_y, weight, mtile_expert, row_align) if need_x else none()
+        d_w = K.gemm_wgrad(d_y, x, weight.size(0), pad_offsets) if need_w else none()
+        d_b = K.bias_grad(d_y, maps) if need_b else none()
+    return d_x, d_w, d_b
+
+
+@moe_expert_linear_backward.register_fake
+def _(d_y, x, weight, pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align, need_x, need_w, need_b):
+    none = lambda: d_y.new_empty(0)  # noqa: E731
+    return (torch.empty_like(x) if need_x else none(), torch.empty_like(weight) if need_w else none(),
+            d_y.new_empty(weight.size(0), weight.size(1)) if need_b else none())  # fmt: skip
+
+
+def _linear_setup(ctx, inputs, output):
+    x, weight, bias, pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align = inputs
+    ctx.save_for_backward(x, weight, pad_offsets, row_of_slot, slot_of_row, mtile_expert)
+    ctx.top_k, ctx.row_align, ctx.has_bias = top_k, row_align, bias is not None
+
+
+def _linear_backward(ctx, d_y):
+    x, weight, pad_offsets, row_of_slot, slot_of_row, mtile_expert = ctx.saved_tensors
+    need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+    need_b = ctx.has_bias and ctx.needs_input_grad[2]
+    d_x, d_w, d_b = moe_expert_linear_backward(d_y, x, weight, pad_offsets, row_of_slot, slot_of_row, mtile_expert,
+                                               ctx.top_k, ctx.row_align, need_x, need_w, need_b)  # fmt: skip
+    return (d_x if need_x else None, d_w if need_w else None, d_b if need_b else None, None, None, None, None, None,
+            None)  # fmt: skip
+
+
+torch.library.register_autograd(f"{LIBRARY_NAME}::moe_expert_linear", _linear_backward, setup_context=_linear_setup)
+
+
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_combine_rows", mutates_args=())
+def moe_combine_rows(expert_out: torch.Tensor, weights: torch.Tensor, pad_offsets: torch.Tensor,
+                     row_of_slot: torch.Tensor, slot_of_row: torch.Tensor, mtile_expert: torch.Tensor,
+                     row_align: int) -> torch.Tensor:
+    T, top_k = weights.shape
+    with torch.cuda.device(expert_out.device):
+        maps = _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align)
+        return K.combine(expert_out.contiguous(), weights.contiguous(), maps, T)
+
+
+@moe_combine_rows.register_fake
+def _(expert_out, weights, pad_offsets, row_of_slot, slot_of_row, mtile_expert, row_align):
+    return expert_out.new_empty(weights.size(0), expert_out.size(1))
+
+
+@torch.library.custom_op(f"{LIBRARY_NAME}::moe_combine_rows_backward", mutates_args=())
+def moe_combine_rows_backward(dy: torch.Tensor, expert_out: torch.Tensor, weights: torch.Tensor,
+                              pad_offsets: torch.Tensor, row_of_slot: torch.Tensor, slot_of_row: torch.Tensor,
+                              mtile_expert: torch.Tensor, row_align: int,
+                              need_weights: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    top_k = weights.size(1)
+    with torch.cuda.device(dy.device):
+        maps = _maps(pad_offsets, row_of_slot, slot_of_row, mtile_expert, top_k, row_align)
+        d_out, d_w = K.combine_backward(dy.contiguous(), expert_out, weights, maps, need_weights)
+    return d_out, (d_w if need_weights else dy.new_empty(0))
+
+
+@moe_combine_rows_backward.register_fake
+def _(dy, expert_out, weights, pad_offsets, row_of_slot, slot_of_row, mtile_expert, row_align, need_weights):
+    return torch.empty_like(expert_out), (torch.empty_like(weights) if need_weights else dy.new_empty(0))
+
+
+def _combine_setup(ctx, inputs, output):
+    expert_out, weights, pad_offsets, row_of_slot, slot_of_row, mtile_expert, row_align = inputs
+    ctx.save_for_backward(expert_out, weights, pad_offsets, row_of_slot, slot_of_row, mtile_expert)
+    ctx.row_align = row_align
+
+
+def _combine_backward(ctx, dy):
+    need_w = ctx.needs_input_grad[1]
+    d_out, d_w = moe_combine_rows_backward(dy, *ctx.saved_tensors, ctx.row_align, need_w)
+    return d_out, (d_w if need_w else None), None, None, None, None, None
+
+
+torch.library.register_autograd(f"{LIBRARY_NAME}::moe_combine_rows", _combine_backward, setup_context=_combine_setup)

@@ -320,13 +320,24 @@ class MoE(nn.Module):
         no Python object crosses an op boundary and nothing is stored on the module."""
         from . import _moe_ops
 
-        if not (self.is_glu and self._act_is_swiglu_packed and self.c_fc.bias is None and self.c_proj.bias is None):
-            raise NotImplementedError("torch.compile covers MoE with swiglu_packed experts and no bias")
         router_logits = self.gate(hidden_states)
         router_weights, selected_experts, route_workspace = _moe_ops.moe_route(router_logits, self.top_k)
-        outputs = _moe_ops.moe_swiglu_experts(hidden_states, router_weights, selected_experts, route_workspace,
-                                              self.c_fc.weight, self.c_proj.weight, K.ROW_ALIGN)  # fmt: skip
-        return outputs[0].view(original_shape), router_logits
+        if self.is_glu and self._act_is_swiglu_packed and self.c_fc.bias is None and self.c_proj.bias is None:
+            outputs = _moe_ops.moe_swiglu_experts(hidden_states, router_weights, selected_experts, route_workspace,
+                                                  self.c_fc.weight, self.c_proj.weight, K.ROW_ALIGN)  # fmt: skip
+            return outputs[0].view(original_shape), router_logits
+        # any other activation / experts with bias: the activation is traced as ordinary code between two
+        # expert-linear ops (the reference compiles its MoE with GLU and GELU activations,
+        # tests/modules/moe_test.py:97-98)
+        _count, pad_offsets, row_of_slot, slot_of_row, mtile_expert = _moe_ops.moe_sort_maps(
+            selected_experts, route_workspace, self.num_experts, K.ROW_ALIGN)  # fmt: skip
+        maps = (pad_offsets, row_of_slot, slot_of_row, mtile_expert)
+        grouped = _moe_ops.moe_scatter_rows(hidden_states, *maps, self.top_k, K.ROW_ALIGN)
+        grouped = _moe_ops.moe_expert_linear(grouped, self.c_fc.weight, self.c_fc.bias, *maps, self.top_k, K.ROW_ALIGN)
+        grouped = self.act(grouped)
+        grouped = _moe_ops.moe_expert_linear(grouped, self.c_proj.weight, self.c_proj.bias, *maps, self.top_k, K.ROW_ALIGN)
+        y = _moe_ops.moe_combine_rows(grouped, router_weights, *maps, K.ROW_ALIGN)
+        return y.view(original_shape), router_logits
 
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
         router_logits = self.gate(hidden_states)

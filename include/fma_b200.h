@@ -298,6 +298,24 @@ int fma_b200_swiglu_backward(const void* gate, int64_t gate_pitch, const void* u
                              void* stream);
 
 /* ======================================================================= */
+/* sequence packing (the op that hands packed tokens to the layer)          */
+/* ======================================================================= */
+/*
+ * pack: packed[t, :] = padded[b, s, :] for every token of the padded batch [B, S, row]; unpack: the inverse,
+ * with the padding rows of `padded` written as zeros (the output needs no zero-fill beforehand).  Sequence b
+ * owns packed rows [cu_seqlens[b], cu_seqlens[b+1]) and sits at the end (pad_left != 0) or the start of its S
+ * positions.  Rows are opaque: row_bytes = bytes of one token's data, a multiple of 16.  cu_seqlens: B+1
+ * unsigned 32-bit or signed 64-bit integers on the device (index_bytes 4 or 8); total = rows of `packed`.
+ * Lengths outside [0, S] and rows outside [0, total) are clamped / skipped, never dereferenced.
+ * Replace pack_unpack_sequence_cuda (fma/ops/sequence_packing/cuda_implementation/kernel.cu:45-137) and the
+ * torch.zeros that precedes its unpack call (fma/ops/sequence_packing/__init__.py:44).
+ */
+int fma_b200_pack_sequence(const void* padded, void* packed, const void* cu_seqlens, int32_t index_bytes, int64_t B,
+                           int64_t S, int64_t total, int64_t row_bytes, int32_t pad_left, void* stream);
+int fma_b200_unpack_sequence(const void* packed, void* padded, const void* cu_seqlens, int32_t index_bytes, int64_t B,
+                             int64_t S, int64_t total, int64_t row_bytes, int32_t pad_left, void* stream);
+
+/* ======================================================================= */
 /* grouped GEMM                                                             */
 /* ======================================================================= */
 /*

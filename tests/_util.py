@@ -8,13 +8,13 @@ import torch
 DEV = "cuda"
 
 # rel-L2 bars from the benchmark specification: bf16 <= 1e-2, fp32 <= 1e-5
-TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2}
-ORACLE_DTYPE = {torch.float32: "f32", torch.bfloat16: "bf16"}
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 2e-3}
+ORACLE_DTYPE = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}
 
 
 def to_np(t: torch.Tensor) -> np.ndarray:
     t = t.detach()
-    if t.dtype == torch.bfloat16:
+    if t.dtype in (torch.bfloat16, torch.float16):
         t = t.float()
     if t.dtype == torch.uint32:
         t = t.to(torch.int64)

@@ -88,6 +88,7 @@ def main() -> None:
     ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds fma/)")
     ap.add_argument("--only-bias", action="store_true",
                     help="write only the fixtures added after the first set (add_bias=True layers, the float16 layer)")
+    ap.add_argument("--only-packing", action="store_true", help="write only the sequence-packing fixture")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -95,6 +96,23 @@ def main() -> None:
     from fma import KernelBackend
 
     torch.set_num_threads(8)
+
+    # ---- pack_sequence / unpack_sequence, torch backend, both padding sides -----------------------
+    cu = torch.tensor([0, 3, 3, 10, 11, 18], dtype=torch.int32)  # includes an empty and a full sequence (S = 7)
+    torch.manual_seed(31)
+    padded = torch.randn(5, 7, 2, 4)
+    packed_in = torch.randn(18, 2, 4)
+    pk = {"cu_seqlens": cu.numpy(), "padded": padded.numpy(), "packed_in": packed_in.numpy()}
+    for side in ("left", "right"):
+        pk[f"packed_{side}"] = fma.pack_sequence(padded, cu, padding_side=side, kernel_backend_forward=KernelBackend.torch,
+                                                 kernel_backend_backward=KernelBackend.torch).numpy()
+        pk[f"unpacked_{side}"] = fma.unpack_sequence(packed_in, cu, (5, 7, 2, 4), padding_side=side,
+                                                     kernel_backend_forward=KernelBackend.torch,
+                                                     kernel_backend_backward=KernelBackend.torch).numpy()
+    np.savez_compressed(HERE / "sequence_packing.npz", **pk)
+    print("sequence_packing", {k: v.shape for k, v in pk.items()})
+    if args.only_packing:
+        return
 
     # ---- layer with per-expert biases (add_bias=True) ------------------------------------------
     biased = {
@@ -106,7 +124,7 @@ def main() -> None:
         meta = {k: (str(v) if isinstance(v, torch.dtype) else v) for k, v in cfg.items()}
         np.savez_compressed(HERE / f"{name}.npz", meta=json.dumps(meta), **out)
         print(name, {k: v.shape for k, v in out.items() if k in ("y", "dx", "d_b_fc")})
-    # ---- layer in float16 (the reference's ops are dtype-generic; the kernels of this repository are not yet) ----
+    # ---- layer in float16 (the reference's ops are dtype-generic: fma/include/dtypes/fp16.h) ----
     out, _ = run_layer(fma, T=96, H=64, E=8, k=2, I=32, dtype=torch.float16, seed=17)
     cfg16 = dict(T=96, H=64, E=8, k=2, I=32, dtype=str(torch.float16), seed=17)
     np.savez_compressed(HERE / "layer_f16_small.npz", meta=json.dumps(cfg16), **out)

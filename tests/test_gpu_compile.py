@@ -95,3 +95,48 @@ def test_moe_layer_compiled_fullgraph():
     else:  # the compiler chose another GEMM for the router: near-ties may route differently
         for a, b in zip(eager, compiled):
             assert float((a.float() - b.float()).norm() / b.float().norm()) <= 1e-2
+
+
+@pytest.mark.parametrize("case", ["gelu", "glu", "swiglu_bias"])
+def test_moe_layer_compiled_fullgraph_other_experts(case):
+    """torch.compile(fullgraph=True) of layers whose experts do not take the fused SwiGLU path: a non-gated
+    tanh-GELU, torch's GLU (the two activations of the reference's MoE test, tests/test_commons.py:85-86) and
+    SwiGLU experts with bias.  The activation is traced as ordinary code between two expert-linear ops."""
+    import torch.nn.functional as F
+
+    import fma_b200
+    from fma_b200 import _native
+
+    T, H, E, k, I = 384, 256, 8, 2, 128
+    dtype = torch.bfloat16
+    act, is_glu, bias = {
+        "gelu": (lambda t: F.gelu(t, approximate="tanh"), False, False),
+        "glu": (lambda t: F.glu(t, dim=-1), True, False),
+        "swiglu_bias": (fma_b200.swiglu_packed, True, True),
+    }[case]
+    moe = fma_b200.MoE(E, k, H, I, act, is_glu, bias, 0.02)
+    with torch.no_grad():
+        moe.gate.weight.copy_(randn((E, H), torch.float32, 1, 0.02))
+        moe.c_fc.weight.copy_(randn(tuple(moe.c_fc.weight.shape), torch.float32, 2, 0.02))
+        moe.c_proj.weight.copy_(randn((E, H, I), torch.float32, 3, 0.02))
+        if bias:
+            moe.c_fc.bias.copy_(randn(tuple(moe.c_fc.bias.shape), torch.float32, 6, 0.1))
+            moe.c_proj.bias.copy_(randn((E, H), torch.float32, 7, 0.1))
+    moe = moe.to(DEV).to(dtype)
+    x = randn((T, H), dtype, 4).to(DEV)
+    g = randn((T, H), dtype, 5).to(DEV)
+
+    def run(fn):
+        for p in moe.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        y, logits = fn(xi)
+        y.backward(g)
+        return [y.detach(), logits.detach(), xi.grad] + [p.grad.clone() for p in moe.parameters()]
+
+    eager = run(moe)
+    compiled = run(torch.compile(moe, fullgraph=True))
+    assert _native.device_status() == 0
+    for a, b in zip(eager, compiled):
+        assert a.shape == b.shape
+        assert float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30)) <= 1e-2

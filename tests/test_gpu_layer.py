@@ -57,11 +57,18 @@ def _compare_with_oracle(moe, x, g, dtype, k, tol, y, logits, dx):
     return errs
 
 
-@pytest.mark.parametrize("name", ["layer_f32_small", "layer_f32_k1", "layer_bf16_small", "layer_bf16_many_experts"])
+def _meta_dtype(meta):
+    return {"torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}.get(meta["dtype"], torch.float32)
+
+
+@pytest.mark.parametrize("name", ["layer_f32_small", "layer_f32_k1", "layer_bf16_small", "layer_bf16_many_experts",
+                                  "layer_f16_small"])
 def test_golden_cases(golden_dir, name):
+    """Reference-generated fixtures (fp32, bf16 and IEEE half: the reference's MoE test runs all three,
+    tests/modules/moe_test.py:40-61)."""
     z = np.load(golden_dir / f"{name}.npz")
     meta = json.loads(str(z["meta"]))
-    dtype = torch.bfloat16 if "bfloat16" in meta["dtype"] else torch.float32
+    dtype = _meta_dtype(meta)
     E, k, H, I = meta["E"], meta["k"], meta["H"], meta["I"]
     moe = _build(E, k, H, I, dtype, torch.from_numpy(z["w_gate"]), torch.from_numpy(z["w_fc"]), torch.from_numpy(z["w_proj"]))
     x = torch.from_numpy(z["x"]).to(dtype)
@@ -72,7 +79,7 @@ def test_golden_cases(golden_dir, name):
     # directly against the reference's outputs when both routed identically
     _, sel, _ = O.topk_softmax(to_np(logits), k, ORACLE_DTYPE[dtype])
     if np.array_equal(sel, z["selected"]):
-        direct_tol = 2e-5 if dtype == torch.float32 else 1e-2
+        direct_tol = {torch.float32: 2e-5, torch.bfloat16: 1e-2, torch.float16: 2e-3}[dtype]
         assert rel_l2(to_np(y), z["y"]) <= direct_tol
         assert rel_l2(to_np(dx), z["dx"]) <= direct_tol
         assert rel_l2(to_np(moe.c_fc.weight.grad), z["d_w_fc"]) <= direct_tol
@@ -132,6 +139,18 @@ def test_config1_fp32_full_size(golden_dir):
     for key, arr in (("y", y), ("dx", dx), ("d_w_fc", moe.c_fc.weight.grad), ("d_w_proj", moe.c_proj.weight.grad)):
         a = to_np(arr).astype(np.float64)
         assert abs(np.linalg.norm(a) - stats[key]["l2"]) <= 2e-5 * stats[key]["l2"], key
+
+
+@pytest.mark.parametrize("T,H,E,k,I", [(2048, 512, 8, 2, 1024), (300, 128, 6, 3, 72)])
+def test_f16_against_oracle(T, H, E, k, I):
+    """IEEE half through the same tensor-core kernels (operand format field of the MMA descriptor, half
+    conversions in the epilogues and the row movers)."""
+    dtype = torch.float16
+    w_gate, w_fc, w_proj = randn((E, H), dtype, 1, 0.02), randn((E, 2 * I, H), dtype, 2, 0.02), randn((E, H, I), dtype, 3, 0.02)
+    moe = _build(E, k, H, I, dtype, w_gate, w_fc, w_proj)
+    x, g = randn((T, H), dtype, 4), randn((T, H), dtype, 5)
+    y, logits, dx = _run(moe, x, g)
+    _compare_with_oracle(moe, x, g, dtype, k, TOL[dtype], y, logits, dx)
 
 
 @pytest.mark.parametrize("T,H,E,k,I", [(2048, 512, 8, 2, 1024), (1024, 256, 32, 4, 128), (300, 128, 6, 3, 72), (1, 64, 4, 2, 64)])

@@ -177,3 +177,13 @@ def test_bf16_round_matches_torch():
     x = torch.randn(10000) * 37
     want = x.to(torch.bfloat16).float().numpy()
     np.testing.assert_array_equal(O.bf16_round(x.numpy()), want)
+
+
+@pytest.mark.parametrize("side", ["left", "right"])
+def test_sequence_packing_matches_reference(golden_dir, side):
+    """pack_sequence / unpack_sequence of the oracle against the reference's torch backend (fixture generated
+    by importing the reference): exact copies, zeros in the padding."""
+    z = np.load(golden_dir / "sequence_packing.npz")
+    np.testing.assert_array_equal(O.pack_sequence(z["padded"], z["cu_seqlens"], side), z[f"packed_{side}"])
+    np.testing.assert_array_equal(O.unpack_sequence(z["packed_in"], z["cu_seqlens"], (5, 7, 2, 4), side),
+                                  z[f"unpacked_{side}"])
