@@ -379,9 +379,11 @@ def measure_count(peaks: dict, steps: int, warmup: int, variants=(0,), big: bool
             gbs = (n * 4 + E * 4) / ms / 1e6
             results[f"{dist_name}/variant{variant}"] = {"ms": ms, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]}
         if dist_name == "uniform":
-            # Floor of this measurement: a library reduction that only reads the same 64 MB (torch.sum), and a
-            # kernel that does nothing, both timed the same way (events around one launch behind a busy GPU).
-            for label, fn in (("read_only_sum", lambda i: copies[i % n_copies].sum()),
+            # Floors of this measurement, timed the same way (events around one launch behind a busy GPU): a
+            # library copy of the same 64 MB into a resident buffer (reads AND writes 64 MB), and a kernel that
+            # does nothing (what the two event records and the launch cost by themselves).
+            scratch = torch.empty_like(copies[0])
+            for label, fn in (("copy_64MB", lambda i: scratch.copy_(copies[i % n_copies])),
                               ("empty_launch", lambda i: torch.cuda._sleep(1))):
                 times = []
                 for i in range(warmup + steps):
@@ -394,7 +396,7 @@ def measure_count(peaks: dict, steps: int, warmup: int, variants=(0,), big: bool
                     if i >= warmup:
                         times.append(a.elapsed_time(b))
                 ms = float(np.median(times))
-                results[f"floor/{label}"] = {"ms": ms, "gbs": (n * 4) / ms / 1e6 if label == "read_only_sum" else None}
+                results[f"floor/{label}"] = {"ms": ms}
         del copies
     if big:
         # streaming rate on an input 16x larger (1 GiB of ids), default variant: shows the size-independent part

@@ -17,11 +17,11 @@ int tc_general(const void* A, const void* B, void* D, const uint32_t* M, const u
                int n_groups, bool a_t, bool b_t, void* workspace, int64_t workspace_bytes, cudaStream_t s);
 int64_t tc_general_workspace_bytes(int n_groups, int64_t total_mtiles);
 int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-                const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s);
+                const int32_t* mtile_expert, bool f16, cudaStream_t s);
 int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                       const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s);
+                       const int32_t* mtile_expert, bool f16, cudaStream_t s);
 int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* mtile_expert, bool swiglu, bool narrow, bool f16, cudaStream_t s);
+              const int32_t* mtile_expert, bool swiglu, bool f16, cudaStream_t s);
 int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, int OUT, int IN,
               const int32_t* seg_offsets, int n_seg, bool f16, cudaStream_t s);
 int tc2_forward_peer(const void* X, const void* W, const uint64_t* dst_table, int64_t rows_cap, int E, int OUT, int IN,
@@ -50,20 +50,7 @@ static int pairs_mode() {
 }
 static bool use_pairs(int32_t row_align) { return pairs_mode() >= 1 && row_align > 0 && row_align % 256 == 0; }
 
-// Measurement knob FMA_B200_GEMM_NARROW (bit mask, default 0 = off): the pair kernels with 256x256 tiles whose
-// two tensor-memory halves belong to consecutive tiles.  Bit 0: the two SwiGLU-epilogue GEMMs, bit 1: the
-// plain forward GEMM, bit 2: the plain dgrad GEMM.  Measured slower than the 256x512 tiles at every
-// benchmarked shape except the plain forward GEMM with K = 768.
-static int narrow_mask() {
-    static int v = -1;
-    if (v < 0) {
-        const char* env = getenv("FMA_B200_GEMM_NARROW");
-        v = env ? (atoi(env) & 7) : 0;
-    }
-    return v;
-}
-
-static bool pairs_for_fused_epilogues() { return pairs_mode() == 2 || (narrow_mask() & 1); }
+static bool pairs_for_fused_epilogues() { return pairs_mode() == 2; }
 
 static int check_layer_gemm(int32_t dtype, int64_t rows_cap, int32_t E, int32_t OUT, int32_t IN) {
     FMAB_REQUIRE(known_dtype(dtype), FMA_B200_ERR_UNSUPPORTED, "dtype %d", dtype);
@@ -89,7 +76,7 @@ int fma_b200_moe_gemm_forward(const void* X, const void* W, void* Y, int32_t dty
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool f16 = dtype == FMA_B200_F16;
     if (dtype != FMA_B200_F32 && use_pairs(row_align))
-        return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, (narrow_mask() & 2) != 0, f16, s);
+        return tc2_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, f16, s);
     if (dtype != FMA_B200_F32) return tc_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, f16, s);
     return simt_forward(X, W, Y, rows_cap, E, OUT, IN, mtile_expert, s);
 }
@@ -104,7 +91,7 @@ int fma_b200_moe_gemm_dgrad(const void* dY, const void* W, void* dX, int32_t dty
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool f16 = dtype == FMA_B200_F16;
     if (dtype != FMA_B200_F32 && use_pairs(row_align))
-        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, (narrow_mask() & 4) != 0, f16, s);
+        return tc2_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, f16, s);
     if (dtype != FMA_B200_F32) return tc_dgrad(dY, W, dX, nullptr, rows_cap, E, OUT, IN, mtile_expert, false, f16, s);
     return simt_dgrad(dY, W, dX, rows_cap, E, OUT, IN, mtile_expert, s);
 }
@@ -138,7 +125,7 @@ int fma_b200_moe_gemm_forward_swiglu(const void* X, const void* W, void* pre, vo
     FMAB_REQUIRE(aligned16(X) && aligned16(W) && aligned16(act) && aligned16(pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
     if (use_pairs(row_align) && pairs_for_fused_epilogues())
-        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, (narrow_mask() & 1) != 0, f16,
+        return tc2_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, f16,
                                   static_cast<cudaStream_t>(stream));
     return tc_forward_swiglu(X, W, pre, act, rows_cap, E, I, IN, mtile_expert, f16, static_cast<cudaStream_t>(stream));
 }
@@ -156,7 +143,7 @@ int fma_b200_moe_gemm_dgrad_swiglu(const void* dY, const void* W, const void* pr
     FMAB_REQUIRE(aligned16(dY) && aligned16(W) && aligned16(pre) && aligned16(d_pre), FMA_B200_ERR_BAD_ARG,
                  "pointers not 16-byte aligned");
     if (use_pairs(row_align) && pairs_for_fused_epilogues())
-        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, (narrow_mask() & 1) != 0, f16,
+        return tc2_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, f16,
                          static_cast<cudaStream_t>(stream));
     return tc_dgrad(dY, W, d_pre, pre, rows_cap, E, OUT, I, mtile_expert, true, f16, static_cast<cudaStream_t>(stream));
 }

@@ -1,5 +1,4 @@
 // bf16 grouped GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256x512 output tile per pair of SMs
-// (HALVES = 2, described below; HALVES = 1 is the 256x256 variant, see PairShape).
 //
 // Why pairs: a 128x256x16 MMA issued by one CTA reads 12 KB of shared memory per 128 tensor-pipe
 // cycles while TMA writes the next operands at the same rate, which together exceed what the
@@ -42,16 +41,14 @@ constexpr int PAIR_B_BYTES = PAIR_B_ROWS * BK * 2;                  // 16 KB
 constexpr int PAIR_THREADS = 320;
 constexpr int PAIR_EPI_WARPS = 8;
 
-// Shape of a pair tile.  HALVES = 2: 256 rows x 512 columns, both 256-column halves of tensor memory belong
-// to ONE tile (A staged once for two halves).  HALVES = 1: 256 rows x 256 columns, the two halves of tensor
-// memory belong to CONSECUTIVE tiles, so a whole epilogue overlaps the next tile's main loop (for long
-// epilogues and short reductions); stages are smaller, so the ring is deeper.
-template <int HALVES>
-struct PairShape {
-    static constexpr int kStages = (HALVES == 2) ? 4 : 6;
-    static constexpr int kStageBytes = A_STAGE_BYTES + HALVES * PAIR_B_BYTES;  // 16 KB + HALVES x 16 KB
-    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
-};
+// A pair tile is 256 rows x 512 columns: both 256-column halves of tensor memory belong to one tile, and every
+// ring stage holds this CTA's A slab and its two B slabs.  (256x256 tiles whose halves belong to consecutive
+// tiles were measured too: the whole epilogue then overlaps the next main loop, but A is staged twice as often,
+// and they were slower at every benchmarked shape.)
+constexpr int HALVES = 2;
+constexpr int PAIR_STAGES = 4;
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + HALVES * PAIR_B_BYTES;  // 16 KB + 2 x 16 KB
+constexpr size_t PAIR_RING_BYTES = static_cast<size_t>(PAIR_STAGES) * PAIR_STAGE_BYTES + 1024;
 // Every epilogue passes its output through shared memory (a 4 KB patch per epilogue warp, behind the operand
 // ring).  Tensor memory hands out an accumulator one row per lane; storing that straight from registers makes
 // every store instruction touch 32 different 128-byte lines.  From the patch the output leaves
@@ -165,7 +162,7 @@ struct PairTile {
 };
 
 // tile -> (pair m-tile, n-tile) with SUPER_M/2 pair m-tiles walked together
-template <bool B_MN, int EPI, int HALVES>
+template <bool B_MN, int EPI>
 __device__ __forceinline__ bool decode_pair_tile(const GemmParams& p, int tile, int n_pair_mtiles, uint32_t rank, PairTile& t) {
     constexpr int kSuper = SUPER_M / 2;
     const int per_super = kSuper * p.n_ntiles;
@@ -178,7 +175,7 @@ __device__ __forceinline__ bool decode_pair_tile(const GemmParams& p, int tile, 
     constexpr int n_step = (EPI == EPI_SWIGLU_FWD) ? BN / 2 : BN;
     t.n0 = nt * HALVES * n_step;
     t.n_step = n_step;
-    t.halves = (HALVES == 2 && t.n0 + n_step < p.n_cols) ? 2 : 1;
+    t.halves = (t.n0 + n_step < p.n_cols) ? 2 : 1;
     t.b_k_base = 0;
     if (p.mode == MODE_ROWS) {
         const int e = __ldg(p.mtile_expert + 2 * pm);  // both 128-row tiles of the pair belong to this expert
@@ -223,11 +220,9 @@ __device__ __forceinline__ void decode_pair_segment(const GemmParams& p, const P
     }
 }
 
-template <bool A_MN, bool B_MN, int EPI, int HALVES>
+template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
-    constexpr int PAIR_STAGES = PairShape<HALVES>::kStages;
-    constexpr int PAIR_STAGE_BYTES = PairShape<HALVES>::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[PAIR_STAGES];   // used in the leader only
     __shared__ __align__(8) uint64_t empty_bar[PAIR_STAGES];  // each CTA waits on its own copy
@@ -321,7 +316,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 }
                 if (tile >= total_tiles) break;
                 PairTile t;
-                if (decode_pair_tile<B_MN, EPI, HALVES>(p, tile, n_pair_mtiles, rank, t)) {
+                if (decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) {
                 for (int s = 0; s < n_seg && alive; ++s) {
                     int a_k0, b_k0, len;
                     decode_pair_segment(p, t, s, a_k0, b_k0, len);
@@ -373,7 +368,6 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_phase = 0;
-            uint32_t tile_count = 0;  // tiles that reached the accumulators (HALVES == 1 alternates halves)
             bool alive = true;
             int sslot = 0;
             uint32_t sphase = 0;
@@ -387,11 +381,9 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 }
                 if (tile < 0) break;
                 PairTile t;
-                if (!decode_pair_tile<B_MN, EPI, HALVES>(p, tile, n_pair_mtiles, rank, t)) continue;
-                // accumulator half and barrier parity of the "half 0" work: with HALVES == 1 tile n uses half
-                // n & 1, whose barriers complete a phase every second tile
-                const int h0 = (HALVES == 1) ? static_cast<int>(tile_count & 1u) : 0;
-                const uint32_t ph0 = (HALVES == 1) ? ((tile_count >> 1) & 1u) : acc_phase;
+                if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
+                constexpr int h0 = 0;
+                const uint32_t ph0 = acc_phase;
                 // k-blocks of the tile (all segments); only their count matters to this warp
                 int nkb = 0;
                 for (int s = 0; s < n_seg; ++s) {
@@ -462,8 +454,8 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     if (t.halves == 2) tc_commit_pair(smem_u32(&acc_full_bar[1]));
                 } else {  // empty reduction: both epilogues write zeros
                     for (int h = 0; h < t.halves && alive; ++h) {
-                        const int hb = (HALVES == 1) ? h0 : h;
-                        const uint32_t phb = (HALVES == 1) ? ph0 : acc_phase;
+                        const int hb = h;
+                        const uint32_t phb = acc_phase;
                         if (!mbar_wait(smem_u32(&acc_empty_bar[hb]), phb ^ 1u, abort_ptr, p.status)) {
                             alive = false;
                             break;
@@ -473,14 +465,13 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     }
                     if (!alive) break;
                 }
-                if (HALVES == 2 && t.halves == 1) {
+                if (t.halves == 1) {
                     // keep half 1's barriers in step with the tile count: pass its phase through unused
                     if (!mbar_wait(smem_u32(&acc_empty_bar[1]), acc_phase ^ 1u, abort_ptr, p.status)) break;
                     mbar_arrive(smem_u32(&acc_full_bar[1]));
                     mbar_arrive_cluster(map_to_rank(smem_u32(&acc_full_bar[1]), 1));
                 }
                 acc_phase ^= 1u;
-                ++tile_count;
             }
         }
     } else {
@@ -489,7 +480,6 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
         const int half = (warp - 2) >> 2;
         const bool f16 = p.f16 != 0;
         uint32_t acc_phase = 0;
-        uint32_t tile_count = 0;
         uint32_t store_seq = 0;  // TMA stores issued by this warp: picks the half of its patch
         int sslot = 0;
         uint32_t sphase = 0;
@@ -504,7 +494,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             }
             if (tile < 0) break;
             PairTile t;
-            if (!decode_pair_tile<B_MN, EPI, HALVES>(p, tile, n_pair_mtiles, rank, t)) continue;
+            if (!decode_pair_tile<B_MN, EPI>(p, tile, n_pair_mtiles, rank, t)) continue;
             bool any_k = false;
             for (int s = 0; s < n_seg; ++s) {
                 int a_k0, b_k0, len;
@@ -536,9 +526,8 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             }
 
             for (int h = 0; h < HALVES; ++h) {
-            // tensor-memory half and barrier parity of this part of the tile (see the MMA warp)
-            const int hs = (HALVES == 1) ? static_cast<int>(tile_count & 1u) : h;
-            const uint32_t phs = (HALVES == 1) ? ((tile_count >> 1) & 1u) : acc_phase;
+            const int hs = h;  // tensor-memory half
+            const uint32_t phs = acc_phase;
             if (!mbar_wait(smem_u32(&acc_full_bar[hs]), phs, abort_ptr, p.status)) {
                 alive = false;
                 break;
@@ -737,7 +726,6 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             }  // halves
             if (!alive) break;
             acc_phase ^= 1u;
-            ++tile_count;
         }
         if (lane == 0) bulk_wait_all();  // TMA stores of this warp (if any) are complete before the CTA retires
     }
@@ -780,11 +768,11 @@ static int encode_rows_output(GemmParams& p, const void* D, int64_t rows_cap, in
     return encode_3d(&p.map_d, D, n_cols, rows_cap, 1, pitch, pitch, 32, 32, p.f16 != 0);
 }
 
-template <bool A_MN, bool B_MN, int EPI, int HALVES = 2>
+template <bool A_MN, bool B_MN, int EPI>
 static int launch_pair(const GemmParams& p, int64_t total_tiles, cudaStream_t s) {
     static bool configured[64] = {false};  // per device: the attribute applies to the current device only
-    auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI, HALVES>;
-    constexpr size_t PAIR_SMEM_BYTES = PairShape<HALVES>::kSmemBytes + PEER_PATCH_TOTAL;
+    auto kernel = gemm_tc2_kernel<A_MN, B_MN, EPI>;
+    constexpr size_t PAIR_SMEM_BYTES = PAIR_RING_BYTES + PEER_PATCH_TOTAL;
     const int dev = current_device_slot();
     FMAB_REQUIRE(dev >= 0, FMA_B200_ERR_LAUNCH, "no current CUDA device with an ordinal below 64");
     if (!configured[dev]) {
@@ -812,7 +800,7 @@ static int fill_pair_common(GemmParams& p) {
 }
 
 int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, int OUT, int IN,
-                const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s) {
+                const int32_t* mtile_expert, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
     p.f16 = f16 ? 1 : 0;
@@ -823,7 +811,7 @@ int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, 
     p.d = static_cast<__nv_bfloat16*>(Y);
     p.ldd = OUT;
     p.n_mtiles = static_cast<int>(rows_cap / BM);
-    const int tile_cols = narrow ? BN : 2 * BN;
+    const int tile_cols = 2 * BN;
     p.n_ntiles = (OUT + tile_cols - 1) / tile_cols;
     p.n_cols = OUT;
     p.k_len = IN;
@@ -831,12 +819,11 @@ int tc2_forward(const void* X, const void* W, void* Y, int64_t rows_cap, int E, 
     p.n_groups = E;
     if (int rc = encode_rows_output(p, Y, rows_cap, OUT, OUT)) return rc;
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
-    if (narrow) return launch_pair<false, false, EPI_PLAIN, 1>(p, total, s);
     return launch_pair<false, false, EPI_PLAIN>(p, total, s);
 }
 
 int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64_t rows_cap, int E, int I, int IN,
-                       const int32_t* mtile_expert, bool narrow, bool f16, cudaStream_t s) {
+                       const int32_t* mtile_expert, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
     p.f16 = f16 ? 1 : 0;
@@ -849,19 +836,18 @@ int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64
     p.ldd = I;
     p.inter = I;
     p.n_mtiles = static_cast<int>(rows_cap / BM);
-    const int tile_cols = narrow ? BN / 2 : BN;  // 128 act columns per accumulator half
+    const int tile_cols = BN;  // 128 act columns per accumulator half
     p.n_ntiles = (I + tile_cols - 1) / tile_cols;
     p.n_cols = I;
     p.k_len = IN;
     p.b_group_stride = 2 * I;
     p.n_groups = E;
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
-    if (narrow) return launch_pair<false, false, EPI_SWIGLU_FWD, 1>(p, total, s);
     return launch_pair<false, false, EPI_SWIGLU_FWD>(p, total, s);
 }
 
 int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t rows_cap, int E, int OUT, int IN,
-              const int32_t* mtile_expert, bool swiglu, bool narrow, bool f16, cudaStream_t s) {
+              const int32_t* mtile_expert, bool swiglu, bool f16, cudaStream_t s) {
     GemmParams p;
     if (int rc = fill_pair_common(p)) return rc;
     p.f16 = f16 ? 1 : 0;
@@ -874,7 +860,7 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     p.ldd = swiglu ? 2 * static_cast<int64_t>(IN) : IN;
     p.inter = IN;
     p.n_mtiles = static_cast<int>(rows_cap / BM);
-    const int tile_cols = narrow ? BN : 2 * BN;
+    const int tile_cols = 2 * BN;
     p.n_ntiles = (IN + tile_cols - 1) / tile_cols;
     p.n_cols = IN;
     p.k_len = OUT;
@@ -885,10 +871,6 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     } else {
         }
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
-    if (narrow) {
-        if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD, 1>(p, total, s);
-        return launch_pair<false, true, EPI_PLAIN, 1>(p, total, s);
-    }
     if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD>(p, total, s);
     return launch_pair<false, true, EPI_PLAIN>(p, total, s);
 }

@@ -84,11 +84,14 @@ def pack_sequence(
     if not is_list:
         inputs = [inputs]
     outputs = []
+    total = None
     for x in inputs:
-        if output_shape is None:
-            # one host read of the token count for all tensors, as the reference does
-            output_shape = (int(cu_seqlens[-1].item()), *x.size()[2:])
-        outputs.append(_PackSequence.apply(x, cu_seqlens, tuple(output_shape), padding_side))
+        shape = output_shape
+        if shape is None:
+            if total is None:  # one host read of the token count for all tensors, as the reference does
+                total = int(cu_seqlens[-1].item())
+            shape = (total, *x.size()[2:])
+        outputs.append(_PackSequence.apply(x, cu_seqlens, tuple(shape), padding_side))
     return outputs if is_list else outputs[0]
 
 

@@ -2,8 +2,9 @@
 
 The kernel's three roles - TMA producer (both CTAs), MMA issuer (leader) and 2 x 8 epilogue warps - are
 restated as Python generators that perform the same barrier operations in the same order as the CUDA code,
-for both tile shapes (HALVES = 2: one 256x512 tile owns both tensor-memory halves, half 1 trails half 0 by
-`skew` k-blocks; HALVES = 1: consecutive 256x256 tiles alternate between the halves).  Asynchronous
+for the kernel's tile shape (one 256x512 tile owns both tensor-memory halves, half 1 trails half 0 by `skew`
+k-blocks) and for the 256x256 shape that was measured against it and dropped from the kernel (consecutive tiles
+alternate between the halves; kept here because the model is the record of why that protocol is sound).  Asynchronous
 completions (TMA bytes landing, tcgen05.commit arrivals) are delivered at random later times.  A random
 scheduler interleaves everything and the model checks
   * liveness: every role finishes (no wait that nothing satisfies),
