@@ -31,8 +31,9 @@ from typing import Callable
 import torch
 import torch.distributed as dist
 
+from .. import _native
 from . import _kernels as K
-from .moe import MoE, _is_swiglu_packed
+from .moe import MoE, _Combine, _is_swiglu_packed, _Scatter
 
 ROW_ALIGN = K.ROW_ALIGN
 # transport="auto" uses the peer-memory transport up to this group size and NCCL all-to-all above it.
@@ -296,6 +297,72 @@ class _EPFusedSwigluExperts(torch.autograd.Function):
         return d_x, d_w, d_w_fc, d_w_proj, None, None, None, None
 
 
+class _AllToAllRows(torch.autograd.Function):
+    """Row exchange with a gradient: rows [0, sum(in_splits)) of the input go out, the result has `out_rows`
+    rows of which the first sum(out_splits) are filled; the backward pass is the reverse exchange."""
+
+    @staticmethod
+    def forward(ctx, rows, in_splits, out_splits, out_rows, group):
+        ctx.in_splits, ctx.out_splits, ctx.group, ctx.in_rows = in_splits, out_splits, group, rows.size(0)
+        got = all_to_all_rows(rows.contiguous(), in_splits, out_splits, group)
+        if got.size(0) == out_rows:
+            return got
+        out = torch.zeros(out_rows, rows.size(1), dtype=rows.dtype, device=rows.device)
+        out[: got.size(0)] = got
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        got = all_to_all_rows(d_out.contiguous(), ctx.out_splits, ctx.in_splits, ctx.group)
+        if got.size(0) != ctx.in_rows:
+            d_in = torch.zeros(ctx.in_rows, d_out.size(1), dtype=d_out.dtype, device=d_out.device)
+            d_in[: got.size(0)] = got
+            got = d_in
+        return got, None, None, None, None
+
+
+class _ExpertLinearReceived(torch.autograd.Function):
+    """y[p] = x[p] . W[e(p)]^T (+ bias) over rows received from all ranks: the layout is
+    [source rank][local expert] padded segments (`seg_offsets`), so an expert's rows lie in n_seg segments."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, mtile_expert, seg_offsets, n_seg):
+        x, weight = x.contiguous(), weight.contiguous()
+        ctx.save_for_backward(x, weight, mtile_expert, seg_offsets)
+        ctx.n_seg, ctx.has_bias = n_seg, bias is not None
+        if x.size(0) == 0:  # this rank received nothing
+            return x.new_empty(0, weight.size(1))
+        y = K.gemm_forward(x, weight, mtile_expert, ROW_ALIGN)
+        if bias is not None:
+            # every row of a segment, padding included: padding rows of the received layout never reach a result
+            # (the combine reads token rows only, and the gradients of padding rows are zero)
+            all_rows = torch.zeros(x.size(0), dtype=torch.int32, device=x.device)
+            K.call("fma_b200_moe_bias_add", K.ptr(y), K.ptr(bias.contiguous()), K.dtype_code(y.dtype), y.size(0), y.size(1),
+                   K.ptr(mtile_expert), K.ptr(all_rows), K.stream_ptr(y.device))  # fmt: skip
+        return y
+
+    @staticmethod
+    def backward(ctx, d_y):
+        x, weight, mtile_expert, seg_offsets = ctx.saved_tensors
+        d_y = d_y.contiguous()
+        El, n_seg = weight.size(0), ctx.n_seg
+        d_x = None
+        if ctx.needs_input_grad[0]:
+            d_x = K.gemm_dgrad(d_y, weight, mtile_expert, ROW_ALIGN) if d_y.size(0) > 0 else torch.empty_like(x)
+        d_w = K.gemm_wgrad(d_y, x, El, seg_offsets, n_seg=n_seg) if ctx.needs_input_grad[1] else None
+        d_b = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            acc = torch.zeros(El, d_y.size(1), dtype=torch.float32, device=d_y.device)
+            if d_y.size(0) > 0:
+                part = torch.empty(El, d_y.size(1), dtype=d_y.dtype, device=d_y.device)
+                for s in range(n_seg):  # one column-sum pass per source rank's block of segments, in a fixed order
+                    K.call("fma_b200_moe_bias_grad", K.ptr(d_y), K.dtype_code(d_y.dtype), El, d_y.size(1),
+                           K.ptr(seg_offsets[s * El :]), K.ptr(part), K.stream_ptr(d_y.device))  # fmt: skip
+                    acc += part.float()
+            d_b = acc.to(d_y.dtype)
+        return d_x, d_w, d_b, None, None, None
+
+
 def peer_decision(table: list[list[int]], E: int) -> str:
     """What every rank does with the gathered rows [counts (E), rows_cap, arena in use, transport given up,
     status]: "unavailable" if any rank has given the peer transport up, "busy" if any rank's arena is still
@@ -358,10 +425,12 @@ class ExpertParallelMoE(MoE):
     def _compute_experts(self, hidden_states, router_weights, selected_experts):
         if self.ep_size == 1:
             return super()._compute_experts(hidden_states, router_weights, selected_experts)
-        if not (self.is_glu and _is_swiglu_packed(self.act) and self.c_fc.bias is None):
-            raise NotImplementedError("expert parallelism is implemented for SwiGLU experts without bias")
         maps = self._sort_selected(selected_experts)
         self.last_row_maps = maps
+        fused = self.is_glu and _is_swiglu_packed(self.act) and self.c_fc.bias is None and self.c_proj.bias is None
+        if not fused:
+            self.last_transport = "nccl"
+            return self._compute_experts_general(hidden_states, router_weights, maps)
         # "auto" takes the peer-memory transport only for the group size it has been validated on
         use_peer = self.transport == "peer" or (self.transport == "auto" and self.ep_size <= PEER_AUTO_MAX_RANKS)
         if use_peer:  # decided from the configuration alone: every rank enters the gather below or none does
@@ -373,6 +442,31 @@ class ExpertParallelMoE(MoE):
         return _EPFusedSwigluExperts.apply(hidden_states, router_weights, self.c_fc.weight, self.c_proj.weight, maps,
                                            self.process_group, self.ep_size, self.overlap_chunks)  # fmt: skip
 
+    def _compute_experts_general(self, hidden_states, router_weights, maps):
+        """Any activation, optional bias, any dtype: scatter -> all-to-all -> expert linear -> activation ->
+        expert linear -> all-to-all -> combine as separate differentiable steps over NCCL (no chunked overlap;
+        the fused SwiGLU path above is the fast one)."""
+        ws, group, dev = self.ep_size, self.process_group, hidden_states.device
+        El = self.num_local_experts
+        recv_counts = exchange_counts(maps.expert_count, ws, group)
+        both = torch.cat([maps.expert_count.to(torch.int32), recv_counts.reshape(-1), K.device_status_peek(dev)]).tolist()
+        K.raise_for_device_status(both[-1:], "expert-parallel MoE")
+        E = self.num_experts
+        pad = lambda n: (n + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN  # noqa: E731
+        send_rows = [sum(pad(n) for n in both[r * El : (r + 1) * El]) for r in range(ws)]
+        recv_rows = [sum(pad(n) for n in both[E + s * El : E + (s + 1) * El]) for s in range(ws)]
+        n_recv = sum(recv_rows)
+        seg = torch.empty(ws * El + 1, dtype=torch.int32, device=dev)
+        mt = torch.empty(max(n_recv // 128, 1), dtype=torch.int32, device=dev)
+        K.call("fma_b200_moe_ep_recv_maps", K.ptr(recv_counts.contiguous()), ws, El, ROW_ALIGN, n_recv, K.ptr(seg),
+               K.ptr(mt), K.stream_ptr(dev))  # fmt: skip
+        xg = _Scatter.apply(hidden_states, maps)
+        recv = _AllToAllRows.apply(xg, send_rows, recv_rows, n_recv, group)
+        h = _ExpertLinearReceived.apply(recv, self.c_fc.weight, self.c_fc.bias, mt, seg, ws)
+        h = self.act(h)
+        out = _ExpertLinearReceived.apply(h, self.c_proj.weight, self.c_proj.bias, mt, seg, ws)
+        back = _AllToAllRows.apply(out, recv_rows, send_rows, maps.rows_cap, group)
+        return _Combine.apply(back, router_weights, maps, hidden_states.size(0))
 
     def _compute_experts_peer(self, hidden_states, router_weights, maps):
         """The layer over the peer-memory transport, or None when this call has to use NCCL: the arenas
