@@ -145,6 +145,14 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's completed bulk stores (async proxy) before its later ordinary accesses to the same memory.
+__device__ __forceinline__ void fence_async_to_generic() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// 128-bit load that is served from L2: for data that this kernel itself wrote earlier.
+__device__ __forceinline__ uint4 ld_global_cg_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 // Makes this thread's shared-memory writes visible to the async proxy (TMA) before a store is issued.
 __device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 w) {
@@ -317,8 +325,8 @@ inline int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
 
 // 3-D tensor of 16-bit elements {d0 (contiguous), d1, d2} with pitches in elements, boxes of box0 x box1 x 1 whose rows are
 // box0 * 2 = 64 bytes wide, 64-byte swizzle: the output map of the epilogue that stores with TMA.
-inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
-                     uint64_t pitch2, uint32_t box0, uint32_t box1, bool f16 = false) {
+inline int encode_3d_box(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                         uint64_t pitch2, uint32_t box0, uint32_t box1, uint32_t box2, bool f16 = false) {
     EncodeTiledFn fn = encode_fn();
     FMAB_REQUIRE(fn != nullptr, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
     FMAB_REQUIRE(aligned16(base), FMA_B200_ERR_BAD_ARG, "GEMM output is not 16-byte aligned");
@@ -328,7 +336,7 @@ inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d
     FMAB_REQUIRE(d0 >= 1 && d1 >= 1 && d2 >= 1, FMA_B200_ERR_BAD_ARG, "empty tensor for a tensor map");
     const cuuint64_t dims[3] = {d0, d1, d2};
     const cuuint64_t strides[2] = {pitch1 * 2, pitch2 * 2};
-    const cuuint32_t box[3] = {box0, box1, 1};
+    const cuuint32_t box[3] = {box0, box1, box2};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                           const_cast<void*>(base), dims, strides, box, estr,
@@ -336,6 +344,11 @@ inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FMAB_REQUIRE(r == CUDA_SUCCESS, FMA_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
     return FMA_B200_OK;
+}
+
+inline int encode_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                     uint64_t pitch2, uint32_t box0, uint32_t box1, bool f16 = false) {
+    return encode_3d_box(map, base, d0, d1, d2, pitch1, pitch2, box0, box1, 1, f16);
 }
 
 // Scheduler words of the dynamic tile scheduler: 64 pairs per device, handed out round-robin so that

@@ -506,24 +506,13 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             constexpr int kGroups = BN / 64 / 2;       // 64-column groups per warp and accumulator half
             bool alive = true;
 
-            // SwiGLU backward: the saved up / gate values of one 64-column group in line form.  They are fetched
-            // ahead of their use: for the tile's first group before the accumulator is even awaited (the main loop
-            // is still running then), for every later group while the previous one is being computed.
-            uint4 cu[8], cg[8];
+            // The SwiGLU epilogues run in two phases.  Phase 1 is the plain epilogue: the rounded accumulator leaves
+            // through TMA stores (up / gate into `pre`; d_act into the d_up half of the output) and tensor memory is
+            // handed back at once.  Phase 2 reads those values back in line form (they are in L2), does the
+            // elementwise math and writes act, or d_up over d_act and d_gate, while the next tile's main loop is
+            // already running.  Each warp reads back exactly the region it stored itself.
+            const bool two_phase = (EPI == EPI_SWIGLU_BWD) || (EPI == EPI_SWIGLU_FWD && p.d2 != nullptr);
             const int64_t pre_pitch = 2 * static_cast<int64_t>(p.inter);
-            auto bwd_fetch = [&](int h, int g, int it) {
-                const int n0 = t.n0 + h * t.n_step;
-                const int left = min(t.n_step, p.n_cols - n0) - g * 64;
-                const int row = quad * 32 + it * 4 + lr;
-                const bool ok = h < HALVES && lp * 8 < left && row < t.rows_valid;
-                const __nv_bfloat16* src = p.pre + (t.d_row + row) * pre_pitch + n0 + g * 64 + lp * 8;
-                cu[it] = ok ? ld_global_16(src) : make_uint4(0, 0, 0, 0);
-                cg[it] = ok ? ld_global_16(src + p.inter) : make_uint4(0, 0, 0, 0);
-            };
-            if (EPI == EPI_SWIGLU_BWD) {
-#pragma unroll
-                for (int it = 0; it < 8; ++it) bwd_fetch(0, half * kGroups, it);
-            }
 
             for (int h = 0; h < HALVES; ++h) {
             const int hs = h;  // tensor-memory half
@@ -537,22 +526,31 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             const int n0h = t.n0 + h * t.n_step;                 // first D column of this half
             const int n_valid = min(t.n_step, p.n_cols - n0h);   // <= 0: the half carries no columns
 
-            if (EPI == EPI_PLAIN) {
+            if (EPI == EPI_PLAIN || two_phase) {
                 // 32 rows x 32 columns at a time: accumulator -> bf16 -> one half of the warp's patch (64-byte
                 // rows, 64-byte swizzle) -> ONE TMA store issued by lane 0.  The two halves of the patch
                 // alternate, so a store drains while the next piece is converted and written.
-                constexpr int kChunks = BN / 32 / 2;
+                // A warp owns two 64-column pieces of the half: columns [half*128, +128) of the accumulator, or,
+                // with the SwiGLU forward epilogue, the up and the gate columns of act columns [half*64, +64).
                 const int row_c = ((p.mode == MODE_ROWS) ? static_cast<int>(t.d_row) : t.a_mn) + quad * 32;
                 const int grp_c = (p.mode == MODE_ROWS) ? 0 : t.group;
                 const bool rows_here = quad * 32 < t.rows_valid;
 #pragma unroll 1
-                for (int c = half * kChunks; c < (half + 1) * kChunks; c += 2) {
-                    const int cols_left = n_valid - c * 32;
+                for (int j = 0; j < 2; ++j) {
+                    int acc_col, out_col;
+                    if (EPI == EPI_SWIGLU_FWD) {
+                        acc_col = j * (BN / 2) + half * 64;
+                        out_col = n0h + half * 64;
+                    } else {
+                        acc_col = half * (BN / 2) + j * 64;
+                        out_col = n0h + acc_col;
+                    }
+                    const int cols_left = n_valid - (out_col - n0h);
                     if (cols_left <= 0) break;
                     uint32_t ra[32], rb[32];
                     if (any_k) {  // both pieces of the pair are requested before either is awaited
-                        tc_load_32_issue(taddr + c * 32, ra);
-                        if (cols_left > 32) tc_load_32_issue(taddr + c * 32 + 32, rb);
+                        tc_load_32_issue(taddr + acc_col, ra);
+                        if (cols_left > 32) tc_load_32_issue(taddr + acc_col + 32, rb);
                         tc_load_wait();
                     }
 #pragma unroll
@@ -573,7 +571,10 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         fence_smem_to_async();
                         __syncwarp();
                         if (lane == 0 && rows_here) {
-                            tma_store_3d(&p.map_d, sub, n0h + (c + q) * 32, row_c, grp_c);
+                            if (EPI == EPI_SWIGLU_FWD)
+                                tma_store_3d(&p.map_d, sub, out_col + q * 32, j, row_c);  // {column, up | gate, row}
+                            else
+                                tma_store_3d(&p.map_d, sub, out_col + q * 32, row_c, grp_c);
                             bulk_commit();
                         }
                     }
@@ -613,6 +614,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     __syncwarp();
                 }
             } else if (EPI == EPI_SWIGLU_FWD) {
+                // (caller keeps no `pre`: one phase, nothing to read back)
                 // This warp: 32 rows x 64 act columns of the half (up in accumulator columns [0,128), gate in
                 // [128,256)).  up and gate are rounded to bf16 and go through the patch one after the other;
                 // act = up * gate * sigmoid(gate) is computed from the rounded values in line form, and all three
@@ -667,58 +669,6 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     }
                     __syncwarp();
                 }
-            } else {
-                // d_act tile -> d_up, d_gate with the saved up / gate of the same rows and columns.  The math is
-                // elementwise, so it runs in line form: only d_act (rounded to bf16, as the unfused path would
-                // store it) goes through the patch; up and gate were loaded, and d_up and d_gate are stored, as
-                // whole 128-byte row segments.
-#pragma unroll 1
-                for (int g = half * kGroups; g < (half + 1) * kGroups; ++g) {
-                    const int cols_left = n_valid - g * 64;
-                    if (cols_left <= 0) break;
-                    // the group after this one (same half, or the first of the next half)
-                    const bool same_half = g + 1 < (half + 1) * kGroups;
-                    const int nh = same_half ? h : h + 1, ng = same_half ? g + 1 : half * kGroups;
-                    const bool col_ok = lp * 8 < cols_left;
-                    const int col = n0h + g * 64 + lp * 8;
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        float da[32];
-                        if (cols_left > q * 32) {
-                            tc_load_32(taddr + g * 64 + q * 32, da);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) da[i] = 0.f;
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            st_shared_16(patch_addr(patch, lane, q * 4 + k), pack8(da + k * 8, f16));
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int r = it * 4 + lr;
-                        const int row = quad * 32 + r;
-                        float d[8], u[8], gt[8], du[8], dg[8];
-                        unpack8(ld_shared_16(patch_addr(patch, r, lp)), d, f16);
-                        unpack8(cu[it], u, f16);
-                        unpack8(cg[it], gt, f16);
-                        bwd_fetch(nh, ng, it);  // this step's registers are free: refill them for the next group
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float sg = sigmoid_clamped_fast(gt[i]);
-                            const float silu = gt[i] * sg;
-                            du[i] = d[i] * silu;
-                            dg[i] = d[i] * u[i] * (sg + silu * (1.f - sg));
-                        }
-                        if (col_ok && row < t.rows_valid) {
-                            __nv_bfloat16* dst = p.d + (t.d_row + row) * pre_pitch + col;
-                            st_global_16(dst, pack8(du, f16));
-                            st_global_16(dst + p.inter, pack8(dg, f16));
-                        }
-                    }
-                    __syncwarp();
-                }
             }
             tc_fence_before();
             __syncwarp();
@@ -726,6 +676,87 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             }  // halves
             if (!alive) break;
             acc_phase ^= 1u;
+            if (two_phase) {
+                if (lane == 0) {
+                    bulk_wait_all();            // this warp's stores of the tile have been written ...
+                    fence_async_to_generic();   // ... and are ordered before the ordinary loads below
+                }
+                __syncwarp();
+                const bool rows_ok = t.rows_valid > 0;
+#pragma unroll 1
+                for (int h = 0; h < HALVES && rows_ok; ++h) {
+                    const int n0h = t.n0 + h * t.n_step;
+                    const int n_valid = min(t.n_step, p.n_cols - n0h);
+                    if (EPI == EPI_SWIGLU_FWD) {
+                        // 32 rows x 64 act columns: an access covers four rows x 128 bytes
+                        const int lr = lane >> 3, lp = lane & 7;
+                        const int cw = half * 64 + lp * 8;
+                        if (cw >= n_valid) continue;
+                        const int col = n0h + cw;
+#pragma unroll 1
+                        for (int it0 = 0; it0 < 8; it0 += 4) {
+                            uint4 vu[4], vg[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int row = quad * 32 + (it0 + i) * 4 + lr;
+                                const __nv_bfloat16* src = p.d2 + (t.d_row + row) * pre_pitch + col;
+                                const bool ok = row < t.rows_valid;
+                                vu[i] = ok ? ld_global_cg_16(src) : make_uint4(0, 0, 0, 0);
+                                vg[i] = ok ? ld_global_cg_16(src + p.inter) : make_uint4(0, 0, 0, 0);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int row = quad * 32 + (it0 + i) * 4 + lr;
+                                float u[8], g[8];
+                                unpack8(vu[i], u, f16);
+                                unpack8(vg[i], g, f16);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) u[e] = u[e] * g[e] * sigmoid_clamped_fast(g[e]);
+                                if (row < t.rows_valid) st_global_16(p.d + (t.d_row + row) * p.ldd + col, pack8(u, f16));
+                            }
+                        }
+                    } else {
+                        // 32 rows x 128 columns: an access covers two rows x 256 bytes
+                        const int lr = lane >> 4, lp = lane & 15;
+                        const int cw = half * (BN / 2) + lp * 8;
+                        if (cw >= n_valid) continue;
+                        const int col = n0h + cw;
+#pragma unroll 1
+                        for (int it0 = 0; it0 < 16; it0 += 4) {
+                            uint4 vd[4], vu[4], vg[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int row = quad * 32 + (it0 + i) * 2 + lr;
+                                const int64_t at = (t.d_row + row) * pre_pitch + col;
+                                const bool ok = row < t.rows_valid;
+                                vd[i] = ok ? ld_global_cg_16(p.d + at) : make_uint4(0, 0, 0, 0);
+                                vu[i] = ok ? ld_global_16(p.pre + at) : make_uint4(0, 0, 0, 0);
+                                vg[i] = ok ? ld_global_16(p.pre + at + p.inter) : make_uint4(0, 0, 0, 0);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int row = quad * 32 + (it0 + i) * 2 + lr;
+                                float d[8], u[8], gt[8], du[8], dg[8];
+                                unpack8(vd[i], d, f16);
+                                unpack8(vu[i], u, f16);
+                                unpack8(vg[i], gt, f16);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const float sg = sigmoid_clamped_fast(gt[e]);
+                                    const float silu = gt[e] * sg;
+                                    du[e] = d[e] * silu;
+                                    dg[e] = d[e] * u[e] * (sg + silu * (1.f - sg));
+                                }
+                                if (row < t.rows_valid) {
+                                    __nv_bfloat16* dst = p.d + (t.d_row + row) * pre_pitch + col;
+                                    st_global_16(dst, pack8(du, f16));
+                                    st_global_16(dst + p.inter, pack8(dg, f16));
+                                }
+                            }
+                        }
+                    }
+                }
+            }
         }
         if (lane == 0) bulk_wait_all();  // TMA stores of this warp (if any) are complete before the CTA retires
     }
@@ -842,6 +873,11 @@ int tc2_forward_swiglu(const void* X, const void* W, void* pre, void* act, int64
     p.k_len = IN;
     p.b_group_stride = 2 * I;
     p.n_groups = E;
+    if (pre != nullptr) {
+        // `pre` as {I columns, up | gate, rows}: a store that overhangs the up columns is clipped, not written
+        // into the gate columns
+        if (int rc = encode_3d_box(&p.map_d, pre, I, 2, rows_cap, I, 2 * static_cast<uint64_t>(I), 32, 1, 32, f16)) return rc;
+    }
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
     return launch_pair<false, false, EPI_SWIGLU_FWD>(p, total, s);
 }
@@ -866,10 +902,8 @@ int tc2_dgrad(const void* dY, const void* W, void* dX, const void* pre, int64_t 
     p.k_len = OUT;
     p.b_group_stride = OUT;
     p.n_groups = E;
-    if (!swiglu) {
-        if (int rc = encode_rows_output(p, dX, rows_cap, IN, IN)) return rc;
-    } else {
-        }
+    // with SwiGLU backward the d_act tile is parked in the d_up columns of the [rows, 2 IN] output first
+    if (int rc = encode_rows_output(p, dX, rows_cap, IN, swiglu ? 2 * static_cast<int64_t>(IN) : IN)) return rc;
     const int64_t total = static_cast<int64_t>((p.n_mtiles + 1) / 2) * p.n_ntiles;
     if (swiglu) return launch_pair<false, true, EPI_SWIGLU_BWD>(p, total, s);
     return launch_pair<false, true, EPI_PLAIN>(p, total, s);
