@@ -525,6 +525,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t taddr = tmem_base + hs * BN + (static_cast<uint32_t>(quad * 32) << 16);
             const int n0h = t.n0 + h * t.n_step;                 // first D column of this half
             const int n_valid = min(t.n_step, p.n_cols - n0h);   // <= 0: the half carries no columns
+            bool released = false;  // tensor memory of this half already handed back
 
             if (EPI == EPI_PLAIN || two_phase) {
                 // 32 rows x 32 columns at a time: accumulator -> bf16 -> one half of the warp's patch (64-byte
@@ -535,31 +536,42 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                 const int row_c = ((p.mode == MODE_ROWS) ? static_cast<int>(t.d_row) : t.a_mn) + quad * 32;
                 const int grp_c = (p.mode == MODE_ROWS) ? 0 : t.group;
                 const bool rows_here = quad * 32 < t.rows_valid;
-#pragma unroll 1
+                // All of the warp's 128 accumulator columns are fetched and rounded first (64 packed registers per
+                // lane) and tensor memory is handed back right then: the stores below no longer hold up the next
+                // tile's first MMA.
+                uint4 pk[16];
+#pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    int acc_col, out_col;
-                    if (EPI == EPI_SWIGLU_FWD) {
-                        acc_col = j * (BN / 2) + half * 64;
-                        out_col = n0h + half * 64;
-                    } else {
-                        acc_col = half * (BN / 2) + j * 64;
-                        out_col = n0h + acc_col;
-                    }
-                    const int cols_left = n_valid - (out_col - n0h);
-                    if (cols_left <= 0) break;
+                    const int acc_col = (EPI == EPI_SWIGLU_FWD) ? j * (BN / 2) + half * 64 : half * (BN / 2) + j * 64;
                     uint32_t ra[32], rb[32];
                     if (any_k) {  // both pieces of the pair are requested before either is awaited
                         tc_load_32_issue(taddr + acc_col, ra);
-                        if (cols_left > 32) tc_load_32_issue(taddr + acc_col + 32, rb);
+                        tc_load_32_issue(taddr + acc_col + 32, rb);
                         tc_load_wait();
                     }
 #pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float va[8], vb[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            va[i] = any_k ? __uint_as_float(ra[k * 8 + i]) : 0.f;
+                            vb[i] = any_k ? __uint_as_float(rb[k * 8 + i]) : 0.f;
+                        }
+                        pk[j * 8 + k] = pack8(va, f16);
+                        pk[j * 8 + 4 + k] = pack8(vb, f16);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&acc_empty_bar[hs]), 0));  // the leader's barrier
+                released = true;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int out_off = (EPI == EPI_SWIGLU_FWD) ? half * 64 : half * (BN / 2) + j * 64;  // within the half
+                    const int cols_left = n_valid - out_off;
+#pragma unroll
                     for (int q = 0; q < 2; ++q) {
                         if (cols_left <= q * 32) break;
-                        const uint32_t* r = q ? rb : ra;
-                        float v[32];
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = any_k ? __uint_as_float(r[i]) : 0.f;
                         const uint32_t sub = patch + (store_seq & 1u) * (PEER_PATCH_BYTES / 2);
                         ++store_seq;
                         if (lane == 0) bulk_wait_read_but_one();  // the store that last used this half has read it
@@ -567,14 +579,14 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             st_shared_16(sub + lane * 64 + ((static_cast<uint32_t>(k) ^ ((lane >> 1) & 3u)) << 4),
-                                         pack8(v + k * 8, f16));
+                                         pk[j * 8 + q * 4 + k]);
                         fence_smem_to_async();
                         __syncwarp();
                         if (lane == 0 && rows_here) {
                             if (EPI == EPI_SWIGLU_FWD)
-                                tma_store_3d(&p.map_d, sub, out_col + q * 32, j, row_c);  // {column, up | gate, row}
+                                tma_store_3d(&p.map_d, sub, n0h + out_off + q * 32, j, row_c);  // {column, up | gate, row}
                             else
-                                tma_store_3d(&p.map_d, sub, out_col + q * 32, row_c, grp_c);
+                                tma_store_3d(&p.map_d, sub, n0h + out_off + q * 32, row_c, grp_c);
                             bulk_commit();
                         }
                     }
@@ -670,9 +682,11 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     __syncwarp();
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&acc_empty_bar[hs]), 0));  // the leader's barrier
+            if (!released) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(map_to_rank(smem_u32(&acc_empty_bar[hs]), 0));  // the leader's barrier
+            }
             }  // halves
             if (!alive) break;
             acc_phase ^= 1u;
