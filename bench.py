@@ -472,7 +472,7 @@ def measure_device_steps(layer, x, dy, steps: int, warmup: int, barrier):
 # dram__bytes_write.sum per launch from ncu captures at T = 8192, 16384 and 32768 tokens with all other
 # dimensions of the workload; the traffic is linear in T - a constant for the weights plus a per-token part - and
 # the fit through the two larger sizes, which predicts the smallest within 3 %, is evaluated at T = 65536).
-GEMM_DRAM_TRAFFIC_EP_C5 = 78.4e9
+GEMM_DRAM_TRAFFIC_EP_C5 = 75.1e9
 
 
 def roofline_accounting(cfg: dict, kernel_times: dict, steps: int, ms_step: float, peaks: dict, peaks_kind: str):
