@@ -263,6 +263,51 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f, bool f16) {
 }
 __device__ __forceinline__ float round16(float x, bool f16) { return f16 ? Elem<__half>::round(x) : round_bf16(x); }
 
+// sigmoid of two values, 1 / (1 + 2^(-x log2 e)), with the approximate exp2 and reciprocal instructions and packed
+// fp32 arithmetic.  No clamp is needed: 2^(+large) is +inf, whose reciprocal is 0, and 2^(-large) is 0.
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float2 sigmoid2_fast(float2 x) {
+    const float2 t = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+    const float2 d = __fadd2_rn(make_float2(ex2_approx(t.x), ex2_approx(t.y)), make_float2(1.f, 1.f));
+    return make_float2(rcp_approx(d.x), rcp_approx(d.y));
+}
+// act = up * gate * sigmoid(gate) on 8 values (two at a time)
+__device__ __forceinline__ void swiglu_fwd8(const float* u, const float* g, float* act) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const float2 g2 = make_float2(g[e], g[e + 1]);
+        const float2 r = __fmul2_rn(__fmul2_rn(make_float2(u[e], u[e + 1]), g2), sigmoid2_fast(g2));
+        act[e] = r.x;
+        act[e + 1] = r.y;
+    }
+}
+// d_up = d * silu(gate);  d_gate = d * up * (s + silu(gate) * (1 - s)),  s = sigmoid(gate)
+__device__ __forceinline__ void swiglu_bwd8(const float* d, const float* u, const float* g, float* du, float* dg) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const float2 g2 = make_float2(g[e], g[e + 1]), d2 = make_float2(d[e], d[e + 1]);
+        const float2 s = sigmoid2_fast(g2);
+        const float2 silu = __fmul2_rn(g2, s);
+        const float2 one_minus_s = __ffma2_rn(s, make_float2(-1.f, -1.f), make_float2(1.f, 1.f));
+        const float2 w = __ffma2_rn(silu, one_minus_s, s);
+        const float2 a = __fmul2_rn(d2, silu);
+        const float2 b = __fmul2_rn(__fmul2_rn(d2, make_float2(u[e], u[e + 1])), w);
+        du[e] = a.x;
+        du[e + 1] = a.y;
+        dg[e] = b.x;
+        dg[e + 1] = b.y;
+    }
+}
+
 // one thread owns one output row, 32 columns at a time
 __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float* v, int cols_left, bool f16) {
 #pragma unroll

@@ -724,8 +724,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                                 float u[8], g[8];
                                 unpack8(vu[i], u, f16);
                                 unpack8(vg[i], g, f16);
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) u[e] = u[e] * g[e] * sigmoid_clamped_fast(g[e]);
+                                swiglu_fwd8(u, g, u);
                                 if (row < t.rows_valid) st_global_16(p.d + (t.d_row + row) * p.ldd + col, pack8(u, f16));
                             }
                         }
@@ -754,13 +753,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                                 unpack8(vd[i], d, f16);
                                 unpack8(vu[i], u, f16);
                                 unpack8(vg[i], gt, f16);
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const float sg = sigmoid_clamped_fast(gt[e]);
-                                    const float silu = gt[e] * sg;
-                                    du[e] = d[e] * silu;
-                                    dg[e] = d[e] * u[e] * (sg + silu * (1.f - sg));
-                                }
+                                swiglu_bwd8(d, u, gt, du, dg);
                                 if (row < t.rows_valid) {
                                     __nv_bfloat16* dst = p.d + (t.d_row + row) * pre_pitch + col;
                                     st_global_16(dst, pack8(du, f16));
