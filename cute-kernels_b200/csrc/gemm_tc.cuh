@@ -58,6 +58,7 @@ struct GemmParams {
     const MTileRec* mtiles;
     const int32_t* mtile_expert;  // rows mode
     const int32_t* seg_offsets;   // wgrad mode: [n_seg][E] (+1)
+    const int32_t* group_order;   // wgrad mode, CTA-pair kernel: experts in the order their tiles are handed out, or null
     __nv_bfloat16* d;             // output (act for SWIGLU_FWD, d_pre for SWIGLU_BWD)
     __nv_bfloat16* d2;            // SWIGLU_FWD: pre (may be null)
     const __nv_bfloat16* pre;     // SWIGLU_BWD: saved pre-activations

@@ -196,8 +196,11 @@ __device__ __forceinline__ bool decode_pair_tile(const GemmParams& p, int tile, 
         }
     } else {  // MODE_WGRAD: pair m-tiles are counted per expert
         const int pairs_per_group = (p.mtiles_per_group + 1) / 2;
-        const int e = pm / pairs_per_group;
-        const int m0 = ((pm - e * pairs_per_group) * 2 + static_cast<int>(rank)) * BM;
+        const int slot = pm / pairs_per_group;
+        // experts with the longest reductions first: a tile's time grows with its expert's row count, and a long
+        // tile handed out last would run alone at the end of the launch
+        const int e = (p.group_order != nullptr) ? __ldg(p.group_order + slot) : slot;
+        const int m0 = ((pm - slot * pairs_per_group) * 2 + static_cast<int>(rank)) * BM;
         t.group = e;
         t.a_mn = m0;
         t.b_mn = t.n0 + static_cast<int>(rank) * PAIR_B_ROWS;
@@ -787,9 +790,48 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
     }
 }
 
+// Experts sorted by their row count over all segments, largest first (ties: lower id first).  One block, one
+// thread per expert.
+constexpr int ORDER_MAX_GROUPS = 1024;
+__global__ void __launch_bounds__(ORDER_MAX_GROUPS) group_order_kernel(const int32_t* __restrict__ seg_offsets,
+                                                                       int n_seg, int n_groups, int32_t* __restrict__ order) {
+    __shared__ int32_t rows[ORDER_MAX_GROUPS];
+    const int e = threadIdx.x;
+    int32_t mine = 0;
+    if (e < n_groups) {
+        for (int s = 0; s < n_seg; ++s) mine += seg_offsets[s * n_groups + e + 1] - seg_offsets[s * n_groups + e];
+        rows[e] = mine;
+    }
+    __syncthreads();
+    if (e < n_groups) {
+        int rank = 0;
+        for (int j = 0; j < n_groups; ++j) {
+            const int32_t other = rows[j];
+            rank += (other > mine || (other == mine && j < e)) ? 1 : 0;
+        }
+        order[rank] = e;
+    }
+}
+// Scratch for the order: 64 slots per device handed out round-robin, like the scheduler words.
+static __device__ int32_t g_group_order[64 * ORDER_MAX_GROUPS];
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
+static int next_order_slot(int32_t** out) {
+    static int32_t* base[64] = {nullptr};
+    static unsigned int seq = 0;
+    const int dev = current_device_slot();
+    FMAB_REQUIRE(dev >= 0, FMA_B200_ERR_LAUNCH, "no current CUDA device with an ordinal below 64");
+    if (base[dev] == nullptr) {
+        void* ptr = nullptr;
+        FMAB_CUDA(cudaGetSymbolAddress(&ptr, g_group_order));
+        base[dev] = static_cast<int32_t*>(ptr);
+    }
+    *out = base[dev] + ORDER_MAX_GROUPS * (__atomic_fetch_add(&seq, 1u, __ATOMIC_RELAXED) % 64u);
+    return FMA_B200_OK;
+}
+
 // k-blocks by which accumulator half 1 trails half 0 (0..2); FMA_B200_GEMM_SKEW overrides the default.
 static int pair_skew() {
     static int v = -1;
@@ -981,6 +1023,13 @@ int tc2_wgrad(const void* dY, const void* X, void* dW, int64_t rows_cap, int E, 
     // dW as {IN, OUT, E}: rows of a tile beyond OUT are clipped, not written into the next expert
     if (int rc = encode_3d(&p.map_d, dW, IN, OUT, E, IN, static_cast<uint64_t>(OUT) * IN, 32, 32, f16)) return rc;
     const int64_t total = static_cast<int64_t>(E) * ((p.mtiles_per_group + 1) / 2) * p.n_ntiles;
+    if (E > 1 && E <= ORDER_MAX_GROUPS && total > 0) {
+        int32_t* order = nullptr;
+        if (int rc = next_order_slot(&order)) return rc;
+        group_order_kernel<<<1, ORDER_MAX_GROUPS, 0, s>>>(seg_offsets, n_seg, E, order);
+        if (int rc = check_launch("grouped GEMM (expert order)")) return rc;
+        p.group_order = order;
+    }
     return launch_pair<true, true, EPI_PLAIN>(p, total, s);
 }
 
