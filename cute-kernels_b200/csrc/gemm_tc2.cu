@@ -699,69 +699,83 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                     fence_async_to_generic();   // ... and are ordered before the ordinary loads below
                 }
                 __syncwarp();
-                const bool rows_ok = t.rows_valid > 0;
-#pragma unroll 1
-                for (int h = 0; h < HALVES && rows_ok; ++h) {
-                    const int n0h = t.n0 + h * t.n_step;
-                    const int n_valid = min(t.n_step, p.n_cols - n0h);
-                    if (EPI == EPI_SWIGLU_FWD) {
-                        // 32 rows x 64 act columns: an access covers four rows x 128 bytes
-                        const int lr = lane >> 3, lp = lane & 7;
-                        const int cw = half * 64 + lp * 8;
-                        if (cw >= n_valid) continue;
-                        const int col = n0h + cw;
-#pragma unroll 1
-                        for (int it0 = 0; it0 < 8; it0 += 4) {
-                            uint4 vu[4], vg[4];
+                // The region is walked in batches of four accesses per lane.  As soon as an access has been unpacked
+                // its registers are refilled with the same access of the next batch, so loads stay in flight while
+                // the math and the stores of the current batch run.
+                if (EPI == EPI_SWIGLU_FWD) {
+                    // per half 32 rows x 64 act columns: an access covers four rows x 128 bytes; 2 x 2 batches
+                    constexpr int kBatches = 2 * HALVES;
+                    const int lr = lane >> 3, lp = lane & 7;
+                    const int cw = half * 64 + lp * 8;
+                    // row of the access and its column (the same in `pre`, pitch 2 I, and in `act`, pitch I)
+                    auto at_of = [&](int b, int i, bool& ok, int& col) -> int64_t {
+                        const int n0h = t.n0 + (b >> 1) * t.n_step;
+                        const int row = quad * 32 + ((b & 1) * 4 + i) * 4 + lr;
+                        ok = b < kBatches && cw < min(t.n_step, p.n_cols - n0h) && row < t.rows_valid;
+                        col = n0h + cw;
+                        return t.d_row + row;
+                    };
+                    uint4 vu[4], vg[4];
+                    auto fetch = [&](int b, int i) {
+                        bool ok;
+                        int col;
+                        const int64_t grow = at_of(b, i, ok, col);
+                        vu[i] = ok ? ld_global_cg_16(p.d2 + grow * pre_pitch + col) : make_uint4(0, 0, 0, 0);
+                        vg[i] = ok ? ld_global_cg_16(p.d2 + grow * pre_pitch + p.inter + col) : make_uint4(0, 0, 0, 0);
+                    };
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int row = quad * 32 + (it0 + i) * 4 + lr;
-                                const __nv_bfloat16* src = p.d2 + (t.d_row + row) * pre_pitch + col;
-                                const bool ok = row < t.rows_valid;
-                                vu[i] = ok ? ld_global_cg_16(src) : make_uint4(0, 0, 0, 0);
-                                vg[i] = ok ? ld_global_cg_16(src + p.inter) : make_uint4(0, 0, 0, 0);
-                            }
+                    for (int i = 0; i < 4; ++i) fetch(0, i);
+#pragma unroll 1
+                    for (int b = 0; b < kBatches; ++b) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int row = quad * 32 + (it0 + i) * 4 + lr;
-                                float u[8], g[8];
-                                unpack8(vu[i], u, f16);
-                                unpack8(vg[i], g, f16);
-                                swiglu_fwd8(u, g, u);
-                                if (row < t.rows_valid) st_global_16(p.d + (t.d_row + row) * p.ldd + col, pack8(u, f16));
-                            }
+                        for (int i = 0; i < 4; ++i) {
+                            bool ok;
+                            int col;
+                            const int64_t grow = at_of(b, i, ok, col);
+                            float u[8], g[8];
+                            unpack8(vu[i], u, f16);
+                            unpack8(vg[i], g, f16);
+                            fetch(b + 1, i);
+                            swiglu_fwd8(u, g, u);
+                            if (ok) st_global_16(p.d + grow * p.ldd + col, pack8(u, f16));
                         }
-                    } else {
-                        // 32 rows x 128 columns: an access covers two rows x 256 bytes
-                        const int lr = lane >> 4, lp = lane & 15;
-                        const int cw = half * (BN / 2) + lp * 8;
-                        if (cw >= n_valid) continue;
-                        const int col = n0h + cw;
+                    }
+                } else {
+                    // per half 32 rows x 128 columns: an access covers two rows x 256 bytes; 2 x 4 batches
+                    constexpr int kBatches = 4 * HALVES;
+                    const int lr = lane >> 4, lp = lane & 15;
+                    const int cw = half * (BN / 2) + lp * 8;
+                    auto at_of = [&](int b, int i, bool& ok) -> int64_t {
+                        const int n0h = t.n0 + (b >> 2) * t.n_step;
+                        const int row = quad * 32 + ((b & 3) * 4 + i) * 2 + lr;
+                        ok = b < kBatches && cw < min(t.n_step, p.n_cols - n0h) && row < t.rows_valid;
+                        return (t.d_row + row) * pre_pitch + n0h + cw;
+                    };
+                    uint4 vd[4], vu[4], vg[4];
+                    auto fetch = [&](int b, int i) {
+                        bool ok;
+                        const int64_t at = at_of(b, i, ok);
+                        vd[i] = ok ? ld_global_cg_16(p.d + at) : make_uint4(0, 0, 0, 0);
+                        vu[i] = ok ? ld_global_16(p.pre + at) : make_uint4(0, 0, 0, 0);
+                        vg[i] = ok ? ld_global_16(p.pre + at + p.inter) : make_uint4(0, 0, 0, 0);
+                    };
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) fetch(0, i);
 #pragma unroll 1
-                        for (int it0 = 0; it0 < 16; it0 += 4) {
-                            uint4 vd[4], vu[4], vg[4];
+                    for (int b = 0; b < kBatches; ++b) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int row = quad * 32 + (it0 + i) * 2 + lr;
-                                const int64_t at = (t.d_row + row) * pre_pitch + col;
-                                const bool ok = row < t.rows_valid;
-                                vd[i] = ok ? ld_global_cg_16(p.d + at) : make_uint4(0, 0, 0, 0);
-                                vu[i] = ok ? ld_global_16(p.pre + at) : make_uint4(0, 0, 0, 0);
-                                vg[i] = ok ? ld_global_16(p.pre + at + p.inter) : make_uint4(0, 0, 0, 0);
-                            }
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int row = quad * 32 + (it0 + i) * 2 + lr;
-                                float d[8], u[8], gt[8], du[8], dg[8];
-                                unpack8(vd[i], d, f16);
-                                unpack8(vu[i], u, f16);
-                                unpack8(vg[i], gt, f16);
-                                swiglu_bwd8(d, u, gt, du, dg);
-                                if (row < t.rows_valid) {
-                                    __nv_bfloat16* dst = p.d + (t.d_row + row) * pre_pitch + col;
-                                    st_global_16(dst, pack8(du, f16));
-                                    st_global_16(dst + p.inter, pack8(dg, f16));
-                                }
+                        for (int i = 0; i < 4; ++i) {
+                            bool ok;
+                            const int64_t at = at_of(b, i, ok);
+                            float d[8], u[8], gt[8], du[8], dg[8];
+                            unpack8(vd[i], d, f16);
+                            unpack8(vu[i], u, f16);
+                            unpack8(vg[i], gt, f16);
+                            fetch(b + 1, i);
+                            swiglu_bwd8(d, u, gt, du, dg);
+                            if (ok) {
+                                st_global_16(p.d + at, pack8(du, f16));
+                                st_global_16(p.d + at + p.inter, pack8(dg, f16));
                             }
                         }
                     }
