@@ -509,7 +509,7 @@ class ExpertParallelMoE(MoE):
                     raise
                 self._peer_unavailable = str(e)
                 return None
-        plan = P.PeerPlan(counts, self.ep_rank, self.overlap_chunks)
+        plan = P.PeerPlan(counts, self.ep_rank, self.overlap_chunks, expert_major=not self.fuse_return)
         if max(plan.total_recv_rows) > arena.recv_cap:  # the same plan on every rank
             return None
         if not self._sm_reserved:

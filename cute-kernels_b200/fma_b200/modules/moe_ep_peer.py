@@ -15,7 +15,10 @@ source and destination offsets of every block are computed on the host by `PeerP
 all ranks.
 
 Arena regions (rows of H elements):
-    recv     rows dispatched to my experts, [chunk][source rank][local expert] padded segments
+    recv     rows dispatched to my experts: expert after expert, inside an expert's block source after source
+             with no padding between sources; the block as a whole is padded to the row alignment (rows of
+             the padding are zeroed by the receiver).  With `expert_major=False` (what the GEMM epilogues that
+             store into the senders' arenas need): [chunk][source rank][local expert] padded segments
     d_out    the same layout for the gradient rows dispatched in the backward pass
     back     expert outputs returned to me, in my own grouped layout (operand of the weighted combine)
     d_xg     gradient rows returned to me in the backward pass, same layout
@@ -81,23 +84,42 @@ def _prefix(values: list[int]) -> list[int]:
 
 class PeerPlan:
     """Where every block of rows goes, from the matrix counts[s][e] = rows that rank s routes to
-    (global) expert e.  Pure host arithmetic, the same on every rank.
+    (global) expert e.  Pure host arithmetic, the same on every rank.  Copies are (peer, dst_row, src_row, n_rows).
 
-    A block is the run of padded expert segments that one source sends to one destination for one
-    chunk of the destination's local experts.  Copies are (peer, dst_row, src_row, n_rows)."""
+    expert_major=True (default): a receiver lays its rows out expert after expert; inside an expert's block the
+    sources follow one another WITHOUT padding and the block is padded to `row_align` once.  One copy per
+    (destination, expert).  The padding a receiver's GEMMs work through is then that of a single-GPU layer
+    (half an alignment per expert) instead of half an alignment per expert AND source.
 
-    def __init__(self, counts: list[list[int]], rank: int, n_chunks: int, row_align: int = ROW_ALIGN):
+    expert_major=False: a block is the run of padded expert segments that one source sends to one destination
+    for one chunk of the destination's local experts, shipped as it is ([chunk][source][expert], every segment
+    padded): one copy per (destination, chunk), and every 128-row tile of the receive layout comes from one
+    sender, which is what GEMM epilogues that store straight into the senders' arenas need."""
+
+    def __init__(self, counts: list[list[int]], rank: int, n_chunks: int, row_align: int = ROW_ALIGN,
+                 expert_major: bool = True):
         ws, E = len(counts), len(counts[0])
         if E % ws:
             raise ValueError(f"{E} experts over {ws} ranks")
         El = E // ws
         self.world_size, self.rank, self.num_local_experts = ws, rank, El
+        self.expert_major = expert_major
         self.bounds = chunk_bounds(El, min(n_chunks, MAX_CHUNKS))
         C = self.n_chunks = len(self.bounds) - 1
         self.counts = counts
         # S[s][e]: first row of expert e in rank s's own grouped layout
         self.S = [_prefix([_pad(n, row_align) for n in row]) for row in counts]
         b = self.bounds
+        self.total_send_rows = self.S[rank][E]
+        if expert_major:
+            # tot[r][j]: rows of r's local expert j over all sources; block[r][j]: first row of its block;
+            # within[r][j][s]: offset of source s inside the block
+            self.tot = [[sum(counts[s][r * El + j] for s in range(ws)) for j in range(El)] for r in range(ws)]
+            self.block = [_prefix([_pad(n, row_align) for n in self.tot[r]]) for r in range(ws)]
+            self.within = [[_prefix([counts[s][r * El + j] for s in range(ws)]) for j in range(El)] for r in range(ws)]
+            self.recv_base = [[self.block[r][b[c]] for c in range(C + 1)] for r in range(ws)]
+            self.total_recv_rows = [self.block[r][El] for r in range(ws)]
+            return
         # rows[s][r][c]: size of the block s -> r, chunk c
         self.rows = [[[self.S[s][r * El + b[c + 1]] - self.S[s][r * El + b[c]] for c in range(C)] for r in range(ws)]
                      for s in range(ws)]  # fmt: skip
@@ -105,7 +127,6 @@ class PeerPlan:
         self.recv_base = [_prefix([sum(self.rows[s][r][c] for s in range(ws)) for c in range(C)]) for r in range(ws)]
         self.src_off = [[_prefix([self.rows[s][r][c] for s in range(ws)]) for c in range(C)] for r in range(ws)]
         self.total_recv_rows = [self.recv_base[r][C] for r in range(ws)]
-        self.total_send_rows = self.S[rank][E]
 
     def experts(self, c: int) -> tuple[int, int]:
         return self.bounds[c], self.bounds[c + 1]
@@ -120,15 +141,33 @@ class PeerPlan:
         base = self.recv_base[self.rank]
         return base[c], base[c + 1] - base[c]
 
+    def segments_per_expert(self) -> int:
+        """Row segments an expert's rows form in the receive layout (the weight gradient reduces over them)."""
+        return 1 if self.expert_major else self.world_size
+
+    def padding_ranges(self, c: int) -> list[tuple[int, int]]:
+        """expert_major: [first, end) rows of chunk c in this rank's receive regions that no sender writes (the
+        padding at the end of every expert's block): the receiver zeroes them before its GEMMs read them."""
+        if not self.expert_major:
+            return []
+        me, b = self.rank, self.bounds
+        out = [(self.block[me][j] + self.tot[me][j], self.block[me][j + 1]) for j in range(b[c], b[c + 1])]
+        return [(a, e) for a, e in out if e > a]
+
     def dispatch_copies(self, c: int) -> list[tuple[int, int, int, int]]:
         """My grouped layout -> the receive region of every rank."""
         me, El, b = self.rank, self.num_local_experts, self.bounds
+        if self.expert_major:
+            return [(r, self.block[r][j] + self.within[r][j][me], self.S[me][r * El + j], self.counts[me][r * El + j])
+                    for r in self.peer_order() for j in range(b[c], b[c + 1]) if self.counts[me][r * El + j] > 0]  # fmt: skip
         return [(r, self.recv_base[r][c] + self.src_off[r][c][me], self.S[me][r * El + b[c]], self.rows[me][r][c])
                 for r in self.peer_order()]  # fmt: skip
 
     def return_tiles(self, c: int) -> list[tuple[int, int]]:
         """For every 128-row tile of chunk c in this rank's receive layout: (rank it came from, first row of
         the tile in that rank's grouped layout) - where a fused GEMM epilogue has to store the tile."""
+        if self.expert_major:
+            raise ValueError("per-tile return addresses need expert_major=False: a tile of the packed layout mixes senders")
         me, El = self.rank, self.num_local_experts
         e0, e1 = self.experts(c)
         out = []
@@ -141,6 +180,10 @@ class PeerPlan:
     def return_copies(self, c: int) -> list[tuple[int, int, int, int]]:
         """Rows of my chunk-local result (receive order) -> the grouped layout of the rank they came from."""
         me, El, b = self.rank, self.num_local_experts, self.bounds
+        if self.expert_major:
+            first = self.block[me][b[c]]
+            return [(s, self.S[s][me * El + j], self.block[me][j] - first + self.within[me][j][s], self.counts[s][me * El + j])
+                    for s in self.peer_order() for j in range(b[c], b[c + 1]) if self.counts[s][me * El + j] > 0]  # fmt: skip
         return [(s, self.S[s][me * El + b[c]], self.src_off[me][c][s], self.rows[s][me][c]) for s in self.peer_order()]
 
 
@@ -317,6 +360,12 @@ class PeerArena:
         nbytes = (ctypes.c_int64 * n)(*[k * rb for _, _, _, k in copies])
         _native.call("fma_b200_peer_copy", n, dst, srcs, nbytes, _native.stream_ptr(self.device))
 
+    def zero_rows(self, region: str, ranges: list[tuple[int, int]]) -> None:
+        """Zeroes rows [first, end) of this rank's own region on the current stream (padding no sender writes)."""
+        view = self.regions[region]
+        for first, end in ranges:
+            view[first:end].zero_()
+
     def return_tables(self, plan: PeerPlan) -> tuple[torch.Tensor, list[int]]:
         """Destination addresses for the GEMMs that store into the senders' arenas: an int64 device tensor
         [2, tiles] (row 0: into `back`, row 1: into `d_xg`) over all chunks, and the first tile of every chunk."""
@@ -364,7 +413,14 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
 
         # fuse_return: the down projection (and, in the backward pass, the dgrad) stores its tiles straight
         # into the arenas of the ranks the rows came from, so no result buffer and no return copies exist
+        if fuse_return and plan.expert_major:
+            raise ValueError("fuse_return needs a plan with expert_major=False")
         tables, first_tile = arena.return_tables(plan) if fuse_return else (None, None)
+        n_seg = plan.segments_per_expert()
+        if plan.expert_major:
+            counts_local = counts_dev[:, me * El : (me + 1) * El].sum(0, dtype=torch.int32).reshape(1, El)
+        else:
+            counts_local = counts_dev[:, me * El : (me + 1) * El]
         xg = K.scatter(x, maps)
         ready = torch.cuda.Event()
         ready.record(main)
@@ -385,11 +441,12 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
             e0, e1 = plan.experts(c)
             base, n_rows = plan.recv_chunk(c)
             rows = arena.regions["recv"][base : base + n_rows]
-            counts_c = counts_dev[:, me * El + e0 : me * El + e1].contiguous()
-            seg = torch.empty(ws * (e1 - e0) + 1, dtype=torch.int32, device=dev)
+            counts_c = counts_local[:, e0:e1].contiguous()
+            seg = torch.empty(n_seg * (e1 - e0) + 1, dtype=torch.int32, device=dev)
             mt = torch.empty(max(n_rows // 128, 1), dtype=torch.int32, device=dev)
-            K.call("fma_b200_moe_ep_recv_maps", K.ptr(counts_c), ws, e1 - e0, ROW_ALIGN, n_rows, K.ptr(seg), K.ptr(mt),
+            K.call("fma_b200_moe_ep_recv_maps", K.ptr(counts_c), n_seg, e1 - e0, ROW_ALIGN, n_rows, K.ptr(seg), K.ptr(mt),
                    K.stream_ptr(dev))  # fmt: skip
+            arena.zero_rows("recv", plan.padding_ranges(c))
             arena.wait(FLAG_FWD_DISPATCH, c, seq)
             pre, act = K.gemm_forward_swiglu(rows, w_fc[e0:e1], mt, keep_pre=True)
             if fuse_return:
@@ -456,13 +513,15 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         for c in range(C):
             e0, e1 = plan.experts(c)
             base, n_rows = plan.recv_chunk(c)
+            arena.zero_rows("d_out", plan.padding_ranges(c))
             arena.wait(FLAG_BWD_DISPATCH, c, seq)
             d_out = arena.regions["d_out"][base : base + n_rows]
+            n_seg = plan.segments_per_expert()
             if need_proj:
-                K.gemm_wgrad(d_out, acts[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_proj[e0:e1])
+                K.gemm_wgrad(d_out, acts[c], e1 - e0, seg_offs[c], n_seg=n_seg, out=d_w_proj[e0:e1])
             d_pre = K.gemm_dgrad_swiglu(d_out, w_proj[e0:e1], pres[c], mtiles[c])
             if need_fc:
-                K.gemm_wgrad(d_pre, recv[c], e1 - e0, seg_offs[c], n_seg=ws, out=d_w_fc[e0:e1])
+                K.gemm_wgrad(d_pre, recv[c], e1 - e0, seg_offs[c], n_seg=n_seg, out=d_w_fc[e0:e1])
             if ctx.tables is not None:
                 K.gemm_dgrad_peer(d_pre, w_fc[e0:e1], ctx.tables[1, ctx.first_tile[c] :], mtiles[c])
                 arena.signal(FLAG_BWD_RETURN, c, seq)

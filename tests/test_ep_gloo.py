@@ -103,18 +103,20 @@ def test_shard_and_unshard_state_dict_round_trip():
     local.load_state_dict(sd, strict=True)
 
 
+@pytest.mark.parametrize("expert_major", [True, False])
 @pytest.mark.parametrize("world,E,chunks,align", [(2, 8, 1, 256), (3, 12, 4, 128), (4, 64, 6, 256), (8, 128, 6, 256)])
-def test_peer_plan_routes_every_block(world, E, chunks, align):
-    """Host plan of the peer-memory transport: applying every rank's copy lists to emulated arenas
-    (numpy) must build the [chunk][source][expert] receive layout on each rank, and the return copies
-    must rebuild every sender's own grouped layout."""
+def test_peer_plan_routes_every_block(world, E, chunks, align, expert_major):
+    """Host plan of the peer-memory transport: applying every rank's copy lists to emulated arenas (numpy) must
+    build the receive layout on each rank - expert after expert with the sources packed inside a block and the
+    block padded once (expert_major), or [chunk][source][expert] padded segments - and the return copies must
+    rebuild every sender's own grouped layout."""
     sys.path.insert(0, str(ROOT / "cute-kernels_b200"))
     from fma_b200.modules.moe_ep_peer import PeerPlan
 
     rng = np.random.default_rng(world * 1000 + E)
     counts = rng.choice([0, 1, 7, align - 1, align, align + 1, 3 * align + 5], size=(world, E)).tolist()
     El = E // world
-    plans = [PeerPlan(counts, r, chunks, align) for r in range(world)]
+    plans = [PeerPlan(counts, r, chunks, align, expert_major=expert_major) for r in range(world)]
     pad = lambda n: (n + align - 1) // align * align  # noqa: E731
 
     # every rank's grouped layout: row label = s * 1e9 + e * 1e6 + i, padding rows -1
@@ -132,24 +134,38 @@ def test_peer_plan_routes_every_block(world, E, chunks, align):
     for s in range(world):
         for c in range(plans[s].n_chunks):
             copies = plans[s].dispatch_copies(c)
-            assert sorted(r for r, *_ in copies) == list(range(world)) and copies[-1][0] == s
+            if not expert_major:
+                assert sorted(r for r, *_ in copies) == list(range(world)) and copies[-1][0] == s
             for r, dst, src, n in copies:
+                assert n > 0 or not expert_major
                 assert np.all(recv[r][dst : dst + n] == -7)  # no two blocks overlap
                 recv[r][dst : dst + n] = xg[s][src : src + n]
     for r in range(world):
+        for c in range(plans[r].n_chunks):  # the receiver zeroes what no sender writes
+            for first, end in plans[r].padding_ranges(c):
+                base, n_rows = plans[r].recv_chunk(c)
+                assert base <= first < end <= base + n_rows
+                assert np.all(recv[r][first:end] == -7)
+                recv[r][first:end] = -1
         assert not np.any(recv[r] == -7)  # every row of the receive layout was written
         for c in range(plans[r].n_chunks):
             e0, e1 = plans[r].experts(c)
             base, n_rows = plans[r].recv_chunk(c)
             want = []
-            for s in range(world):
+            if expert_major:
                 for e in range(r * El + e0, r * El + e1):
-                    first = sum(pad(v) for v in counts[s][:e])
-                    want.append(xg[s][first : first + pad(counts[s][e])])
+                    block = [xg[s][sum(pad(v) for v in counts[s][:e]) :][: counts[s][e]] for s in range(world)]
+                    n = sum(b.size for b in block)
+                    want += block + [np.full(pad(n) - n, -1, dtype=np.int64)]
+            else:
+                for s in range(world):
+                    for e in range(r * El + e0, r * El + e1):
+                        first = sum(pad(v) for v in counts[s][:e])
+                        want.append(xg[s][first : first + pad(counts[s][e])])
             want = np.concatenate(want) if want else np.zeros(0, np.int64)
             assert n_rows == want.size and n_rows % 128 == 0
             np.testing.assert_array_equal(recv[r][base : base + n_rows], want)
-    back = [np.full(xg[s].size, -7, dtype=np.int64) for s in range(world)]
+    back = [np.full(xg[s].size, -7 if not expert_major else -1, dtype=np.int64) for s in range(world)]
     for r in range(world):
         for c in range(plans[r].n_chunks):
             base, n_rows = plans[r].recv_chunk(c)
@@ -157,7 +173,11 @@ def test_peer_plan_routes_every_block(world, E, chunks, align):
             for s, dst, src, n in plans[r].return_copies(c):
                 back[s][dst : dst + n] = out[src : src + n]
     for s in range(world):
+        # expert_major returns the token rows only: the padding rows of a sender's layout are never read
         np.testing.assert_array_equal(back[s], xg[s])
+    if expert_major:  # the packed layout is never larger than the per-source padded one
+        other = PeerPlan(counts, 0, chunks, align, expert_major=False)
+        assert all(a <= b for a, b in zip(plans[0].total_recv_rows, other.total_recv_rows))
 
 
 def test_chunk_bounds_cover_all_experts():

@@ -129,6 +129,15 @@ class FakeArena:
 
         return PeerArena.return_tables(self, plan)
 
+    def zero_rows(self, region, ranges):
+        seq = self.seq
+
+        def run():
+            for first, end in ranges:
+                self.row_seq[region][first:end] = seq
+
+        self.sim.enqueue(lambda: True, run, f"zero padding of {region}")
+
     def mark_tiles(self, table, n_tiles, seq):
         """What a GEMM with per-tile destinations does: 128 rows at every address of the table."""
         for addr in table[:n_tiles].tolist():
@@ -257,18 +266,24 @@ def _install(monkeypatch, sim: Sim, arenas: list, plans: list):
     monkeypatch.setattr(K, "gemm_wgrad",
                         lambda dY, X, E, seg, n_seg=1, out=None: kernel(1, "wgrad", **reads_of(dY, X)))
 
-    def combine(back, weights, maps, T):
+    def own_layout_reads(view):
+        """What the row movers read of a region in this rank's own grouped layout: with the packed receive layout
+        only token rows travel back (the kernels never read the padding rows of an expert's segment)."""
         plan = plans[sim.rank]
-        return kernel(T, "combine", arena_reads=[(back, plan.total_send_rows)])
+        if not plan.expert_major:
+            return [(view, plan.total_send_rows)]
+        me = plan.rank
+        return [(view[plan.S[me][e] : plan.S[me][e] + n], None) for e, n in enumerate(plan.counts[me]) if n > 0]
+
+    def combine(back, weights, maps, T):
+        return kernel(T, "combine", arena_reads=own_layout_reads(back))
 
     def combine_backward(dy, back, weights, maps, want):
-        plan = plans[sim.rank]
-        d_back = kernel(maps.rows_cap, "combine backward", arena_reads=[(back, plan.total_send_rows)])
+        d_back = kernel(maps.rows_cap, "combine backward", arena_reads=own_layout_reads(back))
         return d_back, d_back
 
     def scatter_backward(d_xg, maps, T):
-        plan = plans[sim.rank]
-        return kernel(T, "scatter backward", arena_reads=[(d_xg, plan.total_send_rows)])
+        return kernel(T, "scatter backward", arena_reads=own_layout_reads(d_xg))
 
     monkeypatch.setattr(K, "combine", combine)
     monkeypatch.setattr(K, "combine_backward", combine_backward)
@@ -303,7 +318,7 @@ def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts,
         for row in c:
             row[experts - 1] = 0
     send_cap = max(sum(pad(n) for n in row) for c in all_counts for row in c)
-    recv_cap = max(max(PeerPlan(c, 0, chunks, align).total_recv_rows) for c in all_counts)
+    recv_cap = max(max(PeerPlan(c, 0, chunks, align, expert_major=False).total_recv_rows) for c in all_counts)
     for r in range(world):
         arenas.append(FakeArena(sim, r, arenas, send_cap, recv_cap))
     barrier_count = [0] * (n_steps + 1)
@@ -331,7 +346,7 @@ def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts,
         # forward of every rank (host code only enqueues)
         for r in range(world):
             sim.rank = r
-            plans[r] = PeerPlan(counts, r, chunks, align)
+            plans[r] = PeerPlan(counts, r, chunks, align, expert_major=not fuse_return)
             ctxs[r] = FakeCtx()
             x = torch.zeros(5, H)
             P._EPPeerSwigluExperts.forward(ctxs[r], x, torch.zeros(5, 2), torch.zeros(experts // world, 2, H),
