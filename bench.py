@@ -888,6 +888,9 @@ def main() -> None:
     if world > 1 and not args.no_ep_parity:
         ep_parity = ep_parity_check(layer, cfg, rank, world, device, dtype)
 
+    if args.timeline:  # every rank runs the extra step; rank 0 records it
+        write_timeline(args.timeline, lambda: layer_step(layer, x, dy), rank, barrier)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -895,9 +898,6 @@ def main() -> None:
 
     # ---- roofline accounting ----------------------------------------------------------------
     kernels, roofline = roofline_accounting(cfg, kernel_times, args.steps, ms_step, peaks, peaks_kind)
-
-    if args.timeline:
-        write_timeline(args.timeline, lambda: layer_step(layer, x, dy), rank, barrier)
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:

@@ -55,6 +55,16 @@ ARENA_ALLOCATOR = os.environ.get("FMA_B200_PEER_ALLOC", "auto")
 # rank a fault on the others); _allocate_symm refuses an arena that still came with one.
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 _DEBUG = os.environ.get("FMA_B200_PEER_DEBUG", "0") == "1"
+# Helper streams over which the copies of one push are spread (0 = all on the calling stream).
+COPY_STREAMS = int(os.environ.get("FMA_B200_PEER_COPY_STREAMS", "4"))
+_copy_stream_pool: dict[int, list] = {}
+
+
+def _copy_streams(device: torch.device) -> list:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _copy_stream_pool:
+        _copy_stream_pool[idx] = [torch.cuda.Stream(device=device, priority=-1) for _ in range(max(COPY_STREAMS, 0))]
+    return _copy_stream_pool[idx]
 
 
 def _debug(rank: int, text: str) -> None:
@@ -348,17 +358,41 @@ class PeerArena:
     def _flag_index(kind: int, chunk: int, src: int) -> int:
         return (kind * MAX_CHUNKS + chunk) * MAX_RANKS + src
 
-    def push(self, copies: list[tuple[int, int, int, int]], src: torch.Tensor, region: str) -> None:
-        """copies = (peer, dst_row, src_row, n_rows): rows of `src` into `region` of each peer's arena."""
-        copies = [c for c in copies if c[3] > 0]
-        n = len(copies)
-        if n == 0:
-            return
-        rb, base, off = self.row_bytes, src.data_ptr(), self.region_off[region]
+    def _issue(self, copies: list[tuple[int, int, int, int]], base: int, off: int) -> None:
+        n, rb = len(copies), self.row_bytes
         dst = (ctypes.c_uint64 * n)(*[self.peer_ptrs[r] + off + d * rb for r, d, _, _ in copies])
         srcs = (ctypes.c_uint64 * n)(*[base + s * rb for _, _, s, _ in copies])
         nbytes = (ctypes.c_int64 * n)(*[k * rb for _, _, _, k in copies])
         _native.call("fma_b200_peer_copy", n, dst, srcs, nbytes, _native.stream_ptr(self.device))
+
+    def push(self, copies: list[tuple[int, int, int, int]], src: torch.Tensor, region: str) -> None:
+        """copies = (peer, dst_row, src_row, n_rows): rows of `src` into `region` of each peer's arena.
+
+        A copy of a few MB spends as long being set up as moving data (measured: 16 MB peer copies issued one
+        after the other reach 230 GB/s), so a list of more than a few copies is dealt round-robin to
+        COPY_STREAMS helper streams that start after the current stream's work and that the current stream
+        waits for: the copies of the list then overlap one another on different copy engines."""
+        copies = [c for c in copies if c[3] > 0]
+        if not copies:
+            return
+        base, off = src.data_ptr(), self.region_off[region]
+        helpers = _copy_streams(self.device) if len(copies) >= 2 * COPY_STREAMS else []
+        if not helpers:
+            self._issue(copies, base, off)
+            return
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for i, helper in enumerate(helpers):
+            part = copies[i :: len(helpers)]
+            if not part:
+                continue
+            helper.wait_event(start)
+            with torch.cuda.stream(helper):
+                self._issue(part, base, off)
+                done = torch.cuda.Event()
+                done.record(helper)
+            cur.wait_event(done)
 
     def zero_rows(self, region: str, ranges: list[tuple[int, int]]) -> None:
         """Zeroes rows [first, end) of this rank's own region on the current stream (padding no sender writes)."""
