@@ -239,6 +239,23 @@ static int check_rows_args(int32_t dtype, int64_t T, int32_t H, int32_t k) {
 
 }  // namespace fmab
 
+namespace fmab {
+// Zeroes the padding at the end of every segment: rows [seg_offsets[j] + counts[j], seg_offsets[j + 1]).
+// gridDim.y blocks per segment (blockIdx.x = segment); 16-byte stores.
+__global__ void __launch_bounds__(256) zero_padding_kernel(uint8_t* __restrict__ rows, int64_t row_bytes,
+                                                           const int32_t* __restrict__ seg_offsets,
+                                                           const int32_t* __restrict__ counts) {
+    const int j = blockIdx.x;
+    const int64_t first = static_cast<int64_t>(seg_offsets[j]) + counts[j];
+    const int64_t end = seg_offsets[j + 1];
+    if (end <= first) return;
+    uint4* dst = reinterpret_cast<uint4*>(rows + first * row_bytes);
+    const int64_t n = (end - first) * row_bytes / 16;
+    for (int64_t i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.y) * blockDim.x)
+        dst[i] = make_uint4(0, 0, 0, 0);
+}
+}  // namespace fmab
+
 extern "C" {
 
 int fma_b200_moe_scatter(const void* x, int32_t dtype, int64_t T, int32_t H, int32_t k, const int32_t* row_of_slot,
@@ -353,6 +370,21 @@ int fma_b200_moe_bias_grad(const void* d_grouped, int32_t dtype, int32_t E, int3
         bias_grad_kernel<Elt><<<grid, 256, 0, s>>>(static_cast<const Elt*>(d_grouped), C, pad_offsets, static_cast<Elt*>(d_bias));
     });
     return check_launch("moe_bias_grad");
+}
+
+int fma_b200_moe_zero_padding(void* rows, int64_t row_bytes, const int32_t* seg_offsets, const int32_t* counts,
+                               int32_t n_segments, void* stream) {
+    using namespace fmab;
+    FMAB_REQUIRE(n_segments >= 0 && row_bytes > 0 && row_bytes % 16 == 0, FMA_B200_ERR_BAD_ARG,
+                 "n_segments=%d row_bytes=%lld", n_segments, (long long)row_bytes);
+    if (n_segments == 0) return FMA_B200_OK;
+    FMAB_REQUIRE(rows && seg_offsets && counts, FMA_B200_ERR_BAD_ARG, "NULL pointer");
+    FMAB_REQUIRE(aligned16(rows), FMA_B200_ERR_BAD_ARG, "rows are not 16-byte aligned");
+    // enough blocks to fill the GPU whatever the number of segments (a segment's padding is at most a few MB)
+    const int per_segment = n_segments >= 256 ? 1 : (n_segments >= 64 ? 4 : (n_segments >= 16 ? 16 : 32));
+    zero_padding_kernel<<<dim3(n_segments, per_segment), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint8_t*>(rows), row_bytes, seg_offsets, counts);
+    return check_launch("moe_zero_padding");
 }
 
 }  // extern "C"

@@ -55,6 +55,7 @@ SIGNATURES: dict[str, tuple] = {
     ),
     "fma_b200_moe_bias_add": (ctypes.c_int, [_P, _P, _I32, _I64, _I32, _P, _P, _P]),
     "fma_b200_moe_bias_grad": (ctypes.c_int, [_P, _I32, _I32, _I32, _P, _P, _P]),
+    "fma_b200_moe_zero_padding": (ctypes.c_int, [_P, _I64, _P, _P, _I32, _P]),
     "fma_b200_moe_gemm_forward_peer": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
     "fma_b200_moe_gemm_dgrad_peer": (ctypes.c_int, [_P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _I32, _P]),
     "fma_b200_peer_buffer_create": (ctypes.c_int, [_I64, _P, _P]),

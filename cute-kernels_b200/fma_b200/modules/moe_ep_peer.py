@@ -394,11 +394,16 @@ class PeerArena:
                 done.record(helper)
             cur.wait_event(done)
 
-    def zero_rows(self, region: str, ranges: list[tuple[int, int]]) -> None:
-        """Zeroes rows [first, end) of this rank's own region on the current stream (padding no sender writes)."""
-        view = self.regions[region]
-        for first, end in ranges:
-            view[first:end].zero_()
+    def zero_padding(self, region: str, base: int, seg_offsets: torch.Tensor, counts: torch.Tensor,
+                     ranges: list[tuple[int, int]]) -> None:
+        """Zeroes, on the current stream, the rows of this rank's own region that no sender writes: the padding at
+        the end of every expert's block of the chunk that starts at row `base` (`seg_offsets` relative to it,
+        `counts` rows per expert; `ranges` is the same thing as host numbers, for callers that model the arena)."""
+        if not ranges:
+            return
+        view = self.regions[region][base:]
+        K.call("fma_b200_moe_zero_padding", K.ptr(view), self.row_bytes, K.ptr(seg_offsets), K.ptr(counts),
+               counts.numel(), K.stream_ptr(self.device))  # fmt: skip
 
     def return_tables(self, plan: PeerPlan) -> tuple[torch.Tensor, list[int]]:
         """Destination addresses for the GEMMs that store into the senders' arenas: an int64 device tensor
@@ -470,7 +475,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         dispatch(0)
         if C > 1:
             dispatch(1)
-        recv, seg_offs, mtiles, pres, acts = [], [], [], [], []
+        recv, seg_offs, mtiles, pres, acts, chunk_counts = [], [], [], [], [], []
         for c in range(C):
             e0, e1 = plan.experts(c)
             base, n_rows = plan.recv_chunk(c)
@@ -480,7 +485,8 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
             mt = torch.empty(max(n_rows // 128, 1), dtype=torch.int32, device=dev)
             K.call("fma_b200_moe_ep_recv_maps", K.ptr(counts_c), n_seg, e1 - e0, ROW_ALIGN, n_rows, K.ptr(seg), K.ptr(mt),
                    K.stream_ptr(dev))  # fmt: skip
-            arena.zero_rows("recv", plan.padding_ranges(c))
+            if plan.expert_major:
+                arena.zero_padding("recv", base, seg, counts_c, plan.padding_ranges(c))
             arena.wait(FLAG_FWD_DISPATCH, c, seq)
             pre, act = K.gemm_forward_swiglu(rows, w_fc[e0:e1], mt, keep_pre=True)
             if fuse_return:
@@ -498,6 +504,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
             if c + 2 < C:
                 dispatch(c + 2)
             recv.append(rows)
+            chunk_counts.append(counts_c)
             seg_offs.append(seg)
             mtiles.append(mt)
             pres.append(pre)
@@ -509,7 +516,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
 
         if any(ctx.needs_input_grad[:4]):
             ctx.lease = arena.lease()
-        ctx.save_for_backward(back, weights, w_fc, w_proj, *recv, *pres, *acts, *seg_offs, *mtiles)
+        ctx.save_for_backward(back, weights, w_fc, w_proj, *recv, *pres, *acts, *seg_offs, *mtiles, *chunk_counts)
         ctx.maps, ctx.T, ctx.plan, ctx.arena, ctx.seq = maps, T, plan, arena, seq
         ctx.tables, ctx.first_tile = tables, first_tile
         return y
@@ -521,7 +528,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         C, ws, seq = plan.n_chunks, plan.world_size, ctx.seq
         saved = ctx.saved_tensors
         back, weights, w_fc, w_proj = saved[:4]
-        recv, pres, acts, seg_offs, mtiles = (saved[4 + i * C : 4 + (i + 1) * C] for i in range(5))
+        recv, pres, acts, seg_offs, mtiles, chunk_counts = (saved[4 + i * C : 4 + (i + 1) * C] for i in range(6))
         maps = ctx.maps
         dev = dy.device
         main, comm = torch.cuda.current_stream(dev), _comm_stream(dev)
@@ -547,7 +554,8 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         for c in range(C):
             e0, e1 = plan.experts(c)
             base, n_rows = plan.recv_chunk(c)
-            arena.zero_rows("d_out", plan.padding_ranges(c))
+            if plan.expert_major:
+                arena.zero_padding("d_out", base, seg_offs[c], chunk_counts[c], plan.padding_ranges(c))
             arena.wait(FLAG_BWD_DISPATCH, c, seq)
             d_out = arena.regions["d_out"][base : base + n_rows]
             n_seg = plan.segments_per_expert()

@@ -276,6 +276,14 @@ int fma_b200_moe_bias_add(void* grouped, const void* bias, int32_t dtype, int64_
 int fma_b200_moe_bias_grad(const void* d_grouped, int32_t dtype, int32_t E, int32_t C, const int32_t* pad_offsets,
                            void* d_bias, void* stream);
 
+/* Zeroes the padding rows at the end of every segment of a grouped layout that was filled by someone who writes
+ * token rows only (the packed receive layout of the expert-parallel layer): rows
+ * [seg_offsets[j] + counts[j], seg_offsets[j + 1]) for j < n_segments; seg_offsets has n_segments + 1 entries
+ * relative to `rows`, row_bytes is a multiple of 16.  No reference counterpart (the reference zero-fills the whole
+ * padded buffer, modules/moe/cuda_implementation/__init__.py:122-126). */
+int fma_b200_moe_zero_padding(void* rows, int64_t row_bytes, const int32_t* seg_offsets, const int32_t* counts,
+                               int32_t n_segments, void* stream);
+
 /* ======================================================================= */
 /* swiglu                                                                   */
 /* ======================================================================= */

@@ -129,7 +129,7 @@ class FakeArena:
 
         return PeerArena.return_tables(self, plan)
 
-    def zero_rows(self, region, ranges):
+    def zero_padding(self, region, base, seg_offsets, counts, ranges):
         seq = self.seq
 
         def run():
