@@ -97,3 +97,27 @@ def test_expert_bias_add_and_grad(dtype, T, H, E, k):
     got = K.bias_grad(grouped, maps)
     want_g = np.stack([d[ref["pad_offsets"][e] : ref["pad_offsets"][e + 1]].sum(0) for e in range(E)])
     assert rel_l2(to_np(got), want_g) <= (1e-5 if dtype == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("counts", [[5, 0, 300, 256], [1], [255, 257, 511, 0, 0, 3, 1024]])
+def test_zero_padding_rows(dtype, counts):
+    """fma_b200_moe_zero_padding: only the rows between the end of a segment's token rows and the start of the next
+    segment are zeroed; token rows and everything past the last segment stay as they were."""
+    from fma_b200.modules import _kernels as K
+
+    align, H = 256, 72
+    offs = [0]
+    for n in counts:
+        offs.append(offs[-1] + (n + align - 1) // align * align)
+    base, extra = 3, 7  # the layout starts at row `base` of a larger buffer
+    rows = torch.full((base + offs[-1] + extra, H), 1.5, dtype=dtype, device=DEV)
+    seg = torch.tensor(offs, dtype=torch.int32, device=DEV)
+    cnt = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    view = rows[base:]
+    K.call("fma_b200_moe_zero_padding", K.ptr(view), H * rows.element_size(), K.ptr(seg), K.ptr(cnt), len(counts),
+           K.stream_ptr(DEV))  # fmt: skip
+    want = np.full((base + offs[-1] + extra, H), 1.5, dtype=np.float32)
+    for j, n in enumerate(counts):
+        want[base + offs[j] + n : base + offs[j + 1]] = 0
+    np.testing.assert_array_equal(to_np(rows).astype(np.float32), want)
