@@ -825,19 +825,21 @@ def main() -> None:
             def issue_inputs():
                 with torch.cuda.stream(copy_stream):
                     xd = x_host.to(device, non_blocking=True)
-                    dyd = dy_host.to(device, non_blocking=True)
-                    ready = torch.cuda.Event()
-                    ready.record(copy_stream)
-                return xd, dyd, ready
+                    x_ready = torch.cuda.Event()
+                    x_ready.record(copy_stream)
+                    dyd = dy_host.to(device, non_blocking=True)  # only the backward pass needs it
+                    dy_ready = torch.cuda.Event()
+                    dy_ready.record(copy_stream)
+                return xd, dyd, x_ready, dy_ready
 
             nxt = issue_inputs()
             for i in range(n_steps):
-                xd, dyd, ready = nxt
+                xd, dyd, x_ready, dy_ready = nxt
                 if i + 1 < n_steps:
                     nxt = issue_inputs()
                 for p in layer.parameters():
                     p.grad = None
-                main_stream.wait_event(ready)
+                main_stream.wait_event(x_ready)
                 xd.record_stream(main_stream)
                 dyd.record_stream(main_stream)
                 xd.requires_grad_(True)
@@ -848,6 +850,7 @@ def main() -> None:
                     out_stream.wait_event(y_ready)
                     y_host.copy_(y.detach(), non_blocking=True)
                     y.record_stream(out_stream)
+                main_stream.wait_event(dy_ready)
                 y.backward(dyd)
                 dx = xd.grad
                 dx_ready = torch.cuda.Event()
