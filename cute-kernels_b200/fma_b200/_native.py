@@ -111,6 +111,7 @@ KERNELS_PER_CALL = {
     "fma_b200_moe_sort": 3, "fma_b200_moe_sort_routed": 2, "fma_b200_device_status": 0, "fma_b200_device_status_peek": 0, "fma_b200_set_sm_limit": 0, "fma_b200_peer_buffer_create": 0,
     "fma_b200_peer_buffer_open": 0, "fma_b200_peer_buffer_close": 0, "fma_b200_peer_buffer_destroy": 0,
     "fma_b200_peer_copy": 0,
+    "fma_b200_moe_gemm_wgrad": 2,  # expert order + GEMM for the 16-bit types (one kernel for fp32)
 }  # fmt: skip
 launch_count = 0  # kernels launched through this binding since import (a plain counter for benchmarks)
 _timing: dict[str, list] | None = None  # entry point -> [(start event, end event)], when enabled
