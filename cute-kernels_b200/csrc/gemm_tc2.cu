@@ -670,8 +670,7 @@ gemm_tc2_kernel(const __grid_constant__ GemmParams p) {
                         float u[8], g[8];
                         unpack8(lu[it], u, f16);
                         unpack8(lg, g, f16);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) u[i] = u[i] * g[i] * sigmoid_clamped_fast(g[i]);
+                        swiglu_fwd8(u, g, u);
                         if (row < t.rows_valid && lp * 8 < cols_left) {
                             const int64_t grow = t.d_row + row;
                             const int col = n0h + col0 + lp * 8;

@@ -344,6 +344,8 @@ int fma_b200_unpack_sequence(const void* packed, void* padded, const void* cu_se
  * For wgrad under expert parallelism an expert's rows may lie in n_seg segments:
  * seg_offsets is then int32[n_seg*E+1] laid out [segment s][expert e] and
  * pad_offsets is ignored; pass n_seg = 1 and seg_offsets = pad_offsets otherwise.
+ * The 16-bit wgrad hands its tiles out expert by expert in the order of decreasing row count (a tile's reduction
+ * length is its expert's row count; a one-block kernel writes the order into scratch inside the library first).
  * IN and OUT must be multiples of 8; all pointers 16-byte aligned.
  * row_align is the alignment the grouped rows were sorted with (fma_b200_moe_sort's row_align, or the
  * one given to fma_b200_moe_ep_recv_maps): with a multiple of 256 the bf16 kernels run on CTA pairs

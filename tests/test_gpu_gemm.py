@@ -105,6 +105,10 @@ def test_bf16_swiglu_epilogues(counts, I, IN, row_align):
     pad = to_np(maps.slot_of_row)[:total] < 0
     assert np.all(to_np(act[:total])[pad] == 0) and np.all(to_np(pre[:total])[pad] == 0)
 
+    # a caller that keeps no `pre` (inference) gets the same act from the one-phase form of the epilogue
+    none, act_only = K.gemm_forward_swiglu(Xd, Wfcd, maps.mtile_expert, keep_pre=False, row_align=row_align)
+    assert none is None and torch.equal(act_only[:total], act[:total])
+
     d_pre = K.gemm_dgrad_swiglu(dOutd, Wprojd, pre, maps.mtile_expert, row_align)
     d_act = K.gemm_dgrad(dOutd, Wprojd, maps.mtile_expert, 128)
     gg, ug = O.swiglu_backward(to_np(pre[:total, I:]), to_np(pre[:total, :I]), to_np(d_act[:total]), "bf16")
