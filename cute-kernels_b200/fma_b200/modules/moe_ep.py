@@ -37,7 +37,7 @@ from .moe import MoE, _Combine, _is_swiglu_packed, _Scatter
 
 ROW_ALIGN = K.ROW_ALIGN
 # transport="auto" uses the peer-memory transport up to this group size and NCCL all-to-all above it.
-PEER_AUTO_MAX_RANKS = int(os.environ.get("FMA_B200_PEER_AUTO_MAX_RANKS", "4"))
+PEER_AUTO_MAX_RANKS = int(os.environ.get("FMA_B200_PEER_AUTO_MAX_RANKS", "8"))
 
 
 def exchange_counts(expert_count: torch.Tensor, world_size: int, group) -> torch.Tensor:
