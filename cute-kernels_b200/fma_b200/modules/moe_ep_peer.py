@@ -60,6 +60,20 @@ COPY_STREAMS = int(os.environ.get("FMA_B200_PEER_COPY_STREAMS", "8"))
 _copy_stream_pool: dict[int, list] = {}
 
 
+# "2": the dispatch of chunk c+2 is issued behind the return of chunk c on the one side stream (measured on 2, 4
+# and 8 GPUs).  "all": every chunk's dispatch is issued at the start of a pass on a side stream of its own, so a
+# dispatch never queues behind a return that waits for a GEMM (measured on 2 GPUs only: no difference there).
+DISPATCH_AHEAD = os.environ.get("FMA_B200_PEER_DISPATCH_AHEAD", "2")
+_dispatch_streams: dict[int, torch.cuda.Stream] = {}
+
+
+def _dispatch_stream(device: torch.device) -> torch.cuda.Stream:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _dispatch_streams:
+        _dispatch_streams[idx] = torch.cuda.Stream(device=device, priority=-1)
+    return _dispatch_streams[idx]
+
+
 def _copy_streams(device: torch.device) -> list:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _copy_stream_pool:
@@ -467,18 +481,19 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         xg = K.scatter(x, maps)
         ready = torch.cuda.Event()
         ready.record(main)
-        xg.record_stream(comm)
-        with torch.cuda.stream(comm):
-            comm.wait_event(ready)
+        ahead_all = DISPATCH_AHEAD == "all"
+        disp = _dispatch_stream(dev) if ahead_all else comm
+        xg.record_stream(disp)
+        with torch.cuda.stream(disp):
+            disp.wait_event(ready)
 
         def dispatch(c: int) -> None:
-            with torch.cuda.stream(comm):
+            with torch.cuda.stream(disp):
                 arena.push(plan.dispatch_copies(c), xg, "recv")
                 arena.signal(FLAG_FWD_DISPATCH, c, seq)
 
-        dispatch(0)
-        if C > 1:
-            dispatch(1)
+        for c in range(C if ahead_all else min(C, 2)):
+            dispatch(c)
         recv, seg_offs, mtiles, pres, acts, chunk_counts = [], [], [], [], [], []
         for c in range(C):
             e0, e1 = plan.experts(c)
@@ -505,7 +520,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
                     comm.wait_event(done)
                     arena.push(plan.return_copies(c), out, "back")
                     arena.signal(FLAG_FWD_RETURN, c, seq)
-            if c + 2 < C:
+            if not ahead_all and c + 2 < C:
                 dispatch(c + 2)
             recv.append(rows)
             chunk_counts.append(counts_c)
@@ -541,20 +556,21 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
         d_back, d_w = K.combine_backward(dy.contiguous(), back, weights, maps, need_w)
         ready = torch.cuda.Event()
         ready.record(main)
-        d_back.record_stream(comm)
-        with torch.cuda.stream(comm):
-            comm.wait_event(ready)
+        ahead_all = DISPATCH_AHEAD == "all"
+        disp = _dispatch_stream(dev) if ahead_all else comm
+        d_back.record_stream(disp)
+        with torch.cuda.stream(disp):
+            disp.wait_event(ready)
         d_w_fc = torch.empty_like(w_fc) if need_fc else None
         d_w_proj = torch.empty_like(w_proj) if need_proj else None
 
         def dispatch(c: int) -> None:
-            with torch.cuda.stream(comm):
+            with torch.cuda.stream(disp):
                 arena.push(plan.dispatch_copies(c), d_back, "d_out")
                 arena.signal(FLAG_BWD_DISPATCH, c, seq)
 
-        dispatch(0)
-        if C > 1:
-            dispatch(1)
+        for c in range(C if ahead_all else min(C, 2)):
+            dispatch(c)
         for c in range(C):
             e0, e1 = plan.experts(c)
             base, n_rows = plan.recv_chunk(c)
@@ -580,7 +596,7 @@ class _EPPeerSwigluExperts(torch.autograd.Function):
                     comm.wait_event(done)
                     arena.push(plan.return_copies(c), d_recv, "d_xg")
                     arena.signal(FLAG_BWD_RETURN, c, seq)
-            if c + 2 < C:
+            if not ahead_all and c + 2 < C:
                 dispatch(c + 2)
         # every rank waits for all returns even if it needs no input gradient: the peers' pushes into
         # this arena are then complete before the next layer call reuses it

@@ -190,7 +190,7 @@ def _install(monkeypatch, sim: Sim, arenas: list, plans: list):
     """Replaces the CUDA-facing names that moe_ep_peer uses by the simulation's."""
     from fma_b200.modules import moe_ep_peer as P
 
-    streams = {(r, n): FakeStream(sim, r, n) for r in range(sim.world) for n in ("main", "comm")}
+    streams = {(r, n): FakeStream(sim, r, n) for r in range(sim.world) for n in ("main", "comm", "disp")}
 
     class StreamContext:
         def __init__(self, stream):
@@ -207,6 +207,7 @@ def _install(monkeypatch, sim: Sim, arenas: list, plans: list):
     monkeypatch.setattr(torch.cuda, "stream", StreamContext)
     monkeypatch.setattr(torch.cuda, "Event", FakeEvent)
     monkeypatch.setattr(P, "_comm_stream", lambda dev: streams[(sim.rank, "comm")])
+    monkeypatch.setattr(P, "_dispatch_stream", lambda dev: streams[(sim.rank, "disp")])
 
     def kernel(out_rows, what, reads=(), arena_reads=()):
         """A stand-in kernel on the current stream: checks its inputs when it RUNS, then marks its output."""
@@ -298,11 +299,15 @@ class FakeCtx:
         self.saved_tensors = tensors
 
 
+@pytest.mark.parametrize("ahead", ["2", "all"])
 @pytest.mark.parametrize("fuse_return", [False, True])
 @pytest.mark.parametrize("train", [True, False])
 @pytest.mark.parametrize("world,experts,chunks,seed", [(2, 8, 3, 0), (4, 32, 6, 1), (8, 128, 6, 2), (8, 64, 8, 3), (3, 12, 1, 4)])
-def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts, chunks, seed, train, fuse_return):
+def test_peer_transport_program_is_live_and_ordered(monkeypatch, world, experts, chunks, seed, train, fuse_return, ahead):
+    from fma_b200.modules import moe_ep_peer
     from fma_b200.modules.moe_ep_peer import PeerPlan
+
+    monkeypatch.setattr(moe_ep_peer, "DISPATCH_AHEAD", ahead)
 
     rng = np.random.default_rng(seed)
     sim = Sim(world, seed)
